@@ -1,7 +1,7 @@
 """Device memory behind the cache manager's ids.
 
 Per paged group one tensor [layers_in_group, 2 (key, value), pages, kv_heads, page_tokens,
-head_dim] in the compute dtype, zero-filled so that a slot never written holds no NaN (the
+head_dim] in the compute dtype (two tensors, for keys and for values, where their sizes differ), zero-filled so that a slot never written holds no NaN (the
 reference zero-fills too: src/backend/cuda/cuda_backend.cu:757-780).  Per state group one
 tensor [layers_in_group, slots, *state_shape].  A ``LayerCache`` is the view one layer's mixer
 gets.
@@ -30,7 +30,8 @@ def cache_bytes_per_token(needs, dtype: torch.dtype) -> int:
     same number of tokens): keys and values of every layer of the group.  ``needs`` is what
     ``CausalLM.cache_needs`` returns."""
     elem = torch.empty(0, dtype=dtype).element_size()
-    return sum(2 * n.num_kv_heads * n.head_dim * elem for n in needs.values() if n is not None and n.kind in ("full", "window"))
+    return sum(n.num_kv_heads * (n.head_dim + (n.value_dim or n.head_dim)) * elem for n in needs.values()
+               if n is not None and n.kind in ("full", "window"))
 
 
 def state_bytes_per_request(needs) -> int:
@@ -55,6 +56,12 @@ class CacheStorage:
         for g in manager.groups:
             if g.paged:
                 n = g.need
+                if n.value_dim and n.value_dim != n.head_dim:
+                    # values of another size than keys: two tensors [layers, pages, kv_heads, page_tokens, size]
+                    self._paged[g.index] = tuple(
+                        torch.zeros((len(g.layers), max(1, g.pool.n_pages), n.num_kv_heads, g.page_tokens, size),
+                                    dtype=dtype, device=device) for size in (n.head_dim, n.value_dim))
+                    continue
                 self._paged[g.index] = torch.zeros(
                     (len(g.layers), 2, max(1, g.pool.n_pages), n.num_kv_heads, g.page_tokens, n.head_dim),
                     dtype=dtype, device=device)
@@ -72,6 +79,8 @@ class CacheStorage:
         li = g.layers.index(layer)
         if g.paged:
             t = self._paged[gi]
+            if isinstance(t, tuple):
+                return LayerCache(group=gi, page_tokens=g.page_tokens, k=t[0][li], v=t[1][li])
             return LayerCache(group=gi, page_tokens=g.page_tokens, k=t[li, 0], v=t[li, 1])
         return LayerCache(group=gi, page_tokens=g.page_tokens, state=self._state[gi][li])
 
@@ -81,4 +90,5 @@ class CacheStorage:
             t[:, slot].zero_()
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in list(self._paged.values()) + list(self._state.values()))
+        paged = [x for t in self._paged.values() for x in (t if isinstance(t, tuple) else (t,))]
+        return sum(t.numel() * t.element_size() for t in paged + list(self._state.values()))

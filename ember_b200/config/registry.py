@@ -1,6 +1,6 @@
 """One registry from an architecture's name to its configuration class.
 
-``config.json`` names the architecture (``architectures[0]``, else ``model_type``);
+``config.json`` names the architecture (``architectures[0]`` or ``architecture``, else ``model_type``);
 the registered class reads the architecture's own keys and produces a ``ModelSpec``.
 """
 from __future__ import annotations
@@ -31,6 +31,8 @@ def registered_architectures():
 
 def resolve_architecture(config: Mapping) -> str:
     archs = config.get("architectures")
+    if archs is None and isinstance(config.get("architecture"), str):       # some designs name a single one
+        archs = [config["architecture"]]
     if isinstance(archs, (list, tuple)) and archs:
         name = archs[0]
         if name in _ARCHITECTURES:

@@ -37,6 +37,18 @@ class RMSNormSpec(PartSpec):
     eps: float = 1e-6
 
 
+@dataclass(frozen=True)
+class LayerNormSpec(PartSpec):
+    """out = (x - mean) / sqrt(var + eps) * weight + bias, var the mean of the squared deviations.  The tensors are
+    named prefix + ``weight_suffix`` and prefix + ``bias_suffix``."""
+
+    kind: ClassVar[str] = "layernorm"
+    size: int = 0
+    eps: float = 1e-5
+    weight_suffix: str = "weight"
+    bias_suffix: str = "bias"
+
+
 # ---------------------------------------------------------------- position encodings
 @dataclass(frozen=True)
 class RotarySpec(PartSpec):
@@ -46,6 +58,9 @@ class RotarySpec(PartSpec):
     head_dim: int = 0
     rotary_dim: int = 0          # == head_dim for a full rotation
     theta: float = 10000.0
+    # "float32": 1 / powf(theta, 2i / rotary_dim) as the Qwen3 reference computes it; "float64": theta^(-2i / rotary_dim)
+    # in double precision, rounded once
+    frequency_precision: str = "float32"
 
 
 @dataclass(frozen=True)
@@ -83,15 +98,112 @@ class AttentionSpec(PartSpec):
         return self.num_heads // self.num_kv_heads
 
 
+@dataclass(frozen=True)
+class SigmoidAttentionSpec(PartSpec):
+    """Grouped-query causal attention without softmax over a paged cache: a visible key's weight is
+    sigmoid(scale * q . k + head_bias[head]), not normalised over keys.  Keys and values may differ in size; the
+    first ``position.rotary_dim`` elements of query and key heads are rotated.  Tensors: q, k, v, o, pb."""
+
+    kind: ClassVar[str] = "sigmoid_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0             # queries and keys
+    value_dim: int = 0
+    scale: float = 1.0
+    position: PartSpec = field(default_factory=NoPositionSpec)
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec(PartSpec):
+    """Delta-rule memory with a decay per head and key channel: short convolutions + silu on q, k, v, unit-length
+    q and k, a write strength per head, low-rank projections for the decay and for the output gate.
+    ``decay_rank`` / ``gate_rank`` 0: read from the stored tensors' shapes."""
+
+    kind: ClassVar[str] = "channel_delta"
+    hidden_size: int = 0
+    num_heads: int = 0            # value heads
+    num_kv_heads: int = 0         # query/key heads
+    head_dim: int = 0
+    value_dim: int = 0
+    conv_taps: int = 4
+    decay_rank: int = 0
+    gate_rank: int = 0
+    norm_eps: float = 1e-6
+    key_eps: float = 1e-6         # inside the root of the unit norm of q and k
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec(PartSpec):
+    """Matrix memory with an exponential input gate (mLSTM): log gates capped by ``gate_cap * tanh(. / gate_cap)``,
+    a running maximum that starts at zero, per-head RMS norm and a sigmoid output gate."""
+
+    kind: ClassVar[str] = "mlstm"
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    gate_cap: float = 15.0
+    norm_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec(PartSpec):
+    """Selective state space with a scalar decay per head (Mamba-2): one input projection [z | x | B | C | dt], a
+    short convolution + silu over x, B, C, a silu gate before an RMS norm in ``norm_groups`` equal parts."""
+
+    kind: ClassVar[str] = "mamba2"
+    hidden_size: int = 0
+    num_heads: int = 0
+    value_dim: int = 0
+    state_size: int = 0
+    num_groups: int = 1
+    norm_groups: int = 1
+    conv_taps: int = 4
+    norm_eps: float = 1e-6
+
+    @property
+    def inner(self) -> int:
+        return self.num_heads * self.value_dim
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec(PartSpec):
+    """Two mixers that read the same input; the result is left_scale * left + right_scale * right."""
+
+    kind: ClassVar[str] = "parallel"
+    hidden_size: int = 0
+    left: PartSpec = field(default_factory=PartSpec)
+    right: PartSpec = field(default_factory=PartSpec)
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    left_prefix: str = "left."
+    right_prefix: str = "right."
+
+
+# ----------------------------------------------------------------------------- gates
+@dataclass(frozen=True)
+class SigmoidGateSpec(PartSpec):
+    """An element-wise gate sigmoid(W h + b) on a sublayer's result.  Tensors: prefix + ``weight_suffix`` [size,
+    size] and prefix + ``bias_suffix`` [size]."""
+
+    kind: ClassVar[str] = "sigmoid_linear"
+    size: int = 0
+    weight_suffix: str = "weight"
+    bias_suffix: str = "bias"
+
+
 # --------------------------------------------------------------------- feed-forwards
 @dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
-    """down( act(gate(x)) * up(x) ), no biases."""
+    """down( act(gate(x)) * up(x) ), no biases; act is "silu" or "relu".  ``names``: the three tensors' names under
+    the prefix (gate, up, down)."""
 
     kind: ClassVar[str] = "gated_mlp"
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
+    names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
 
 
 # ---------------------------------------------------------------------------- layers

@@ -1,0 +1,195 @@
+// Norms and gates around a sublayer, all statistics in fp32:
+//   layer_norm        out[r] = (x - mean) / sqrt(var + eps) * w + b      (var = mean of squared deviations)
+//   gated_norm_add    residual[r] += norm(y[r] * sigmoid(gate_logits[r])) for a layer norm or an RMS norm
+//   group_norm_gate   a token's row cut into groups, each divided by its own root mean square, times a weight,
+//                     with a gate before (silu) or after (sigmoid) the norm
+//   scaled_sum        out (+)= a x + b y
+//   act_mul           out[m, j] = act(x[m, 2j]) * x[m, 2j + 1] for an unfused gate/up product
+// Rows are read from the fp32 residual stream or from fp32 results of a product; a row is reduced by one block
+// (or one warp for the short rows of a head) in an order fixed by the thread layout.
+#include "common.cuh"
+
+EMBER_DEFINE_LAST_ERROR
+
+namespace ember {
+
+constexpr int ROW_THREADS = 256;
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ------------------------------------------------------------------------------------------ layer norm
+template <typename TO>
+__global__ void __launch_bounds__(ROW_THREADS)
+layer_norm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                  const float* __restrict__ b, float eps, TO* __restrict__ out, int H) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* in = x + (size_t)(rows ? rows[r] : r) * H;
+    TO* o = out + (size_t)r * H;
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS) s += in[i];
+    const float mean = block_sum(s, scratch) / (float)H;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS) {
+        const float d = in[i] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS)
+        o[i] = from_float<TO>((in[i] - mean) * rstd * w[i] + (b ? b[i] : 0.0f));
+}
+
+// ------------------------------------------------------------------------------- gate, norm, add to the stream
+// v = y * sigmoid(gate + gate_bias) (gate nullable); centred (layer norm) or not (RMS norm); residual += v_hat * w + b.
+template <bool CENTRED>
+__global__ void __launch_bounds__(ROW_THREADS)
+gated_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ gate, const float* __restrict__ gate_bias,
+                      const float* __restrict__ w, const float* __restrict__ b, float eps, float* __restrict__ residual, int H) {
+    extern __shared__ float row[];          // H floats: the gated row
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * H;
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS) {
+        float v = y[base + i];
+        if (gate) v *= sigmoidf_(gate[base + i] + (gate_bias ? gate_bias[i] : 0.0f));
+        row[i] = v;
+        s += v;
+    }
+    float mean = 0.0f;
+    if (CENTRED) mean = block_sum(s, scratch) / (float)H;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS) {
+        const float d = row[i] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS)
+        residual[base + i] += (row[i] - mean) * rstd * w[i] + (b ? b[i] : 0.0f);
+}
+
+// ---------------------------------------------------------------------------------- per-group RMS norm with gate
+// One warp per (token, group).  gate_mode 0: none; 1: out *= sigmoid(gate) after the norm; 2: v *= silu(gate) before.
+template <typename TO>
+__global__ void group_norm_gate_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gate, int ldg,
+                                       const float* __restrict__ w, int w_stride, float eps, int gate_mode,
+                                       TO* __restrict__ out, int T, int groups, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= T * groups) return;
+    const int t = warp / groups, g = warp - t * groups;
+    const float* in = x + (size_t)t * ldx + (size_t)g * V;
+    const float* gl = gate ? gate + (size_t)t * ldg + (size_t)g * V : nullptr;
+    float ss = 0.0f;
+    for (int j = lane; j < V; j += 32) {
+        float v = in[j];
+        if (gate_mode == 2) { const float z = gl[j]; v *= z * sigmoidf_(z); }
+        ss = fmaf(v, v, ss);
+    }
+    const float r = 1.0f / sqrtf(warp_sum(ss) / (float)V + eps);
+    TO* o = out + ((size_t)t * groups + g) * V;
+    const float* wg = w + (size_t)g * w_stride;
+    for (int j = lane; j < V; j += 32) {
+        float v = in[j];
+        if (gate_mode == 2) { const float z = gl[j]; v *= z * sigmoidf_(z); }
+        v = v * r * wg[j];
+        if (gate_mode == 1) v *= sigmoidf_(gl[j]);
+        o[j] = from_float<TO>(v);
+    }
+}
+
+__global__ void scaled_sum_kernel(const float* __restrict__ x, float a, const float* __restrict__ y, float b,
+                                  float* __restrict__ out, int accumulate, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = a * x[i] + (y ? b * y[i] : 0.0f);
+    out[i] = accumulate ? out[i] + v : v;
+}
+
+// act 0: silu, 1: relu
+template <typename T>
+__global__ void act_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int act, size_t n_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_out) return;
+    const float g = to_float(x[2 * i]), u = to_float(x[2 * i + 1]);
+    out[i] = from_float<T>((act == 1 ? fmaxf(g, 0.0f) : g / (1.0f + expf(-g))) * u);
+}
+
+}  // namespace ember
+
+using namespace ember;
+
+EMBER_API int ember_layer_norm(const float* x, const int* rows, const float* w, const float* b, float eps, void* out,
+                               int out_dtype, int n_rows, int H, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0) return fail("layer_norm: bad width %d", H);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (out_dtype == EMBER_F32)
+        launch_kernel(layer_norm_kernel<float>, n_rows, ROW_THREADS, 0, st, x, rows, w, b, eps, (float*)out, H);
+    else if (out_dtype == EMBER_BF16)
+        launch_kernel(layer_norm_kernel<__nv_bfloat16>, n_rows, ROW_THREADS, 0, st, x, rows, w, b, eps, (__nv_bfloat16*)out, H);
+    else
+        return fail("layer_norm: unsupported output dtype %d", out_dtype);
+    return check_launch("layer_norm");
+}
+
+EMBER_API int ember_gated_norm_add(const float* y, const float* gate, const float* gate_bias, const float* w, const float* b, float eps, int centred,
+                                   float* residual, int n_rows, int H, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || (size_t)H * 4 > 200 * 1024) return fail("gated_norm_add: width %d is not taken", H);
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(gated_norm_add_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gated_norm_add_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    if (centred) launch_kernel(gated_norm_add_kernel<true>, n_rows, ROW_THREADS, smem, st, y, gate, gate_bias, w, b, eps, residual, H);
+    else launch_kernel(gated_norm_add_kernel<false>, n_rows, ROW_THREADS, smem, st, y, gate, gate_bias, w, b, eps, residual, H);
+    return check_launch("gated_norm_add");
+}
+
+EMBER_API int ember_group_norm_gate(const float* x, int ldx, const float* gate, int ldg, const float* w, int w_stride,
+                                    float eps, int gate_mode, void* out, int out_dtype, int T, int groups, int V, void* stream) {
+    if (T <= 0) return 0;
+    if (groups <= 0 || V <= 0 || ldx < groups * V) return fail("group_norm_gate: %d groups of %d in rows of %d", groups, V, ldx);
+    if (gate_mode < 0 || gate_mode > 2 || (gate_mode && (!gate || ldg < groups * V))) return fail("group_norm_gate: bad gate");
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long warps = (long long)T * groups;
+    const unsigned blocks = (unsigned)((warps + 7) / 8);
+    if (out_dtype == EMBER_F32)
+        launch_kernel(group_norm_gate_kernel<float>, blocks, 256, 0, st, x, ldx, gate, ldg, w, w_stride, eps, gate_mode, (float*)out, T, groups, V);
+    else if (out_dtype == EMBER_BF16)
+        launch_kernel(group_norm_gate_kernel<__nv_bfloat16>, blocks, 256, 0, st, x, ldx, gate, ldg, w, w_stride, eps, gate_mode,
+                      (__nv_bfloat16*)out, T, groups, V);
+    else
+        return fail("group_norm_gate: unsupported output dtype %d", out_dtype);
+    return check_launch("group_norm_gate");
+}
+
+EMBER_API int ember_scaled_sum(const float* x, float a, const float* y, float b, float* out, int accumulate, long long n, void* stream) {
+    if (n <= 0) return 0;
+    launch_kernel(scaled_sum_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, x, a, y, b, out, accumulate, (size_t)n);
+    return check_launch("scaled_sum");
+}
+
+EMBER_API int ember_act_mul_interleaved(const void* x, void* out, int dtype, int act, long long n_out, void* stream) {
+    if (n_out <= 0) return 0;
+    if (act != 0 && act != 1) return fail("act_mul: unknown activation %d", act);
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((n_out + 255) / 256);
+    if (dtype == EMBER_F32)
+        launch_kernel(act_mul_kernel<float>, blocks, 256, 0, st, (const float*)x, (float*)out, act, (size_t)n_out);
+    else if (dtype == EMBER_BF16)
+        launch_kernel(act_mul_kernel<__nv_bfloat16>, blocks, 256, 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, act, (size_t)n_out);
+    else
+        return fail("act_mul: unsupported dtype %d", dtype);
+    return check_launch("act_mul");
+}

@@ -26,6 +26,7 @@ class CausalLM:
         self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_prefix)
         self.embedding_position = build_part("position", spec.embedding_position, spec.embedding_position_prefix)
         self.rt: Optional[Runtime] = None
+        self._cache_subs = [tuple(b.cache_needs()) for b in self.blocks]      # sub-ids of each block's caches
 
     # ------------------------------------------------------------------ weights
     def weight_decls(self) -> List[WeightDecl]:
@@ -108,7 +109,7 @@ class CausalLM:
         for i, e in enumerate(s.schedule):
             owner = e.cache_of if e.cache_of >= 0 else e.layer
             block = self.blocks[e.layer]
-            caches = {sub: storage.layer(self.cache_id(owner, sub)) for sub in block.mixers}
+            caches = {sub: storage.layer(self.cache_id(owner, sub)) for sub in self._cache_subs[e.layer]}
             block.forward(ctx, h, caches, owns_cache=(owner == e.layer))
             if capture is not None:
                 capture[1][i + 1].copy_(h[row])

@@ -549,3 +549,240 @@ def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ou
           c_int(head_dim), _p(tiles), c_int(n_tiles), _p(block_table), c_int(block_table.shape[-1]), c_int(page),
           c_int(k_pool.shape[0]), c_int(window), c_float(scale), c_int(n_splits), c_int(split_keys), _p(part_o),
           _p(part_ml), _p(err), c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
+# ------------------------------------------------ norms and gates around a sublayer (csrc/norm_gate.cu)
+def _stream(stream):
+    return c_void_p(stream if stream is not None else current_stream_ptr())
+
+
+def _off(t: torch.Tensor, elements: int = 0):
+    """Address of element ``elements`` of a device tensor."""
+    return c_void_p(t.data_ptr() + elements * t.element_size())
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out: torch.Tensor,
+               n_rows: int, rows: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """out[r] = (x - mean) / sqrt(var + eps) * weight + bias over x[rows[r] or r]; x fp32, statistics fp32."""
+    _check(x, "x", torch.float32)
+    _check(weight, "weight", torch.float32)
+    _check(out, "out")
+    H = x.shape[-1]
+    if weight.numel() != H or out.shape[-1] != H or out.numel() < n_rows * H or (bias is not None and bias.numel() != H):
+        raise KernelError(f"layer_norm: width {H}, weight {tuple(weight.shape)}, out {tuple(out.shape)} for {n_rows} rows")
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_layer_norm, _p(x), _p(rows), _p(weight), _p(bias), c_float(eps), _p(out), c_int(dtype_code(out.dtype)),
+          c_int(n_rows), c_int(H), _stream(stream))
+
+
+def gated_norm_add(y: torch.Tensor, gate_logits: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
+                   eps: float, centred: bool, residual: torch.Tensor, n_rows: int, gate_bias: Optional[torch.Tensor] = None,
+                   stream: Optional[int] = None) -> None:
+    """residual[r] += norm(y[r] * sigmoid(gate_logits[r] + gate_bias)): a layer norm (``centred``) or an RMS norm,
+    all fp32."""
+    for t, n in ((y, "y"), (weight, "weight"), (residual, "residual")):
+        _check(t, n, torch.float32)
+    H = residual.shape[-1]
+    if y.shape[-1] != H or weight.numel() != H or y.numel() < n_rows * H or residual.numel() < n_rows * H:
+        raise KernelError(f"gated_norm_add: rows of {H}, y {tuple(y.shape)}, weight {tuple(weight.shape)}")
+    if gate_logits is not None:
+        _check(gate_logits, "gate_logits", torch.float32)
+        if gate_logits.shape[-1] != H or gate_logits.numel() < n_rows * H:
+            raise KernelError("gated_norm_add: the gate does not fit the rows")
+    lib = _lib("norm_gate")
+    if gate_bias is not None:
+        _check(gate_bias, "gate_bias", torch.float32)
+        if gate_bias.numel() != H:
+            raise KernelError("gated_norm_add: the gate's bias does not fit the rows")
+    _call(lib, lib.ember_gated_norm_add, _p(y), _p(gate_logits), _p(gate_bias), _p(weight), _p(bias), c_float(eps), c_int(1 if centred else 0),
+          _p(residual), c_int(n_rows), c_int(H), _stream(stream))
+
+
+GATE_NONE, GATE_SIGMOID_AFTER, GATE_SILU_BEFORE = 0, 1, 2
+
+
+def group_norm_gate(x: torch.Tensor, x_col: int, gate: Optional[torch.Tensor], gate_col: int, weight: torch.Tensor,
+                    per_group_weight: bool, eps: float, gate_mode: int, out: torch.Tensor, T: int, groups: int, width: int,
+                    stream: Optional[int] = None) -> None:
+    """A token's ``groups * width`` values (fp32, from column ``x_col`` of x's rows), each group divided by its root
+    mean square and multiplied by ``weight`` (one for all groups or one per group); the gate (fp32 rows, from column
+    ``gate_col``) is a sigmoid after the norm or a silu before it."""
+    _check(x, "x", torch.float32)
+    _check(weight, "weight", torch.float32)
+    _check(out, "out")
+    if x.dim() != 2 or x.shape[0] < T or x_col + groups * width > x.shape[1] or out.numel() < T * groups * width:
+        raise KernelError(f"group_norm_gate: {groups} groups of {width} from column {x_col} of {tuple(x.shape)}")
+    if weight.numel() != (groups * width if per_group_weight else width):
+        raise KernelError(f"group_norm_gate: weight of {weight.numel()} for {groups} groups of {width}")
+    if gate_mode != GATE_NONE:
+        _check(gate, "gate", torch.float32)
+        if gate.dim() != 2 or gate.shape[0] < T or gate_col + groups * width > gate.shape[1]:
+            raise KernelError("group_norm_gate: the gate does not fit")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_group_norm_gate, _off(x, x_col), c_int(x.shape[1]), _off(gate, gate_col) if gate_mode else c_void_p(0),
+          c_int(gate.shape[1] if gate_mode else 0), _p(weight), c_int(width if per_group_weight else 0), c_float(eps),
+          c_int(gate_mode), _p(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(groups), c_int(width), _stream(stream))
+
+
+def scaled_sum(x: torch.Tensor, a: float, y: Optional[torch.Tensor], b: float, out: torch.Tensor, n: int,
+               accumulate: bool = False, stream: Optional[int] = None) -> None:
+    """out[:n] (+)= a * x[:n] + b * y[:n], fp32."""
+    for t, name in ((x, "x"), (out, "out")) + (((y, "y"),) if y is not None else ()):
+        _check(t, name, torch.float32)
+        if t.numel() < n:
+            raise KernelError("scaled_sum: a buffer is too small")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_scaled_sum, _p(x), c_float(a), _p(y), c_float(b), _p(out), c_int(1 if accumulate else 0), c_longlong(n),
+          _stream(stream))
+
+
+ACTIVATIONS = {"silu": 0, "relu": 1}
+
+
+def act_mul_interleaved(x: torch.Tensor, out: torch.Tensor, activation: str, n_out: int, stream: Optional[int] = None) -> None:
+    """out[m, j] = act(x[m, 2j]) * x[m, 2j + 1] for an unfused gate/up product over interleaved rows."""
+    _check(x, "x")
+    _check(out, "out", x.dtype)
+    if activation not in ACTIVATIONS or x.numel() < 2 * n_out or out.numel() < n_out:
+        raise KernelError(f"act_mul: activation {activation!r}, {n_out} outputs")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_act_mul_interleaved, _p(x), _p(out), c_int(dtype_code(x.dtype)), c_int(ACTIVATIONS[activation]),
+          c_longlong(n_out), _stream(stream))
+
+
+# -------------------------------------------------------------------- recurrent mixers (csrc/recurrent.cu)
+def _check_runs(query_start: torch.Tensor, slots: torch.Tensor, S: int) -> None:
+    _check(query_start, "query_start", torch.int32)
+    _check(slots, "slots", torch.int32)
+    if query_start.numel() < S + 1 or slots.numel() < S:
+        raise KernelError("the run arrays are shorter than the step")
+
+
+def conv_silu(x: torch.Tensor, col: int, taps: torch.Tensor, bias: Optional[torch.Tensor], carry: torch.Tensor,
+              carry_col: int, seq_of: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
+              T: int, S: int, stream: Optional[int] = None) -> None:
+    """Short causal convolution per channel + silu over the step's runs.  ``x`` fp32 [T, ld]: channels are its
+    columns col .. col + C; ``taps`` fp32 [C, n] (the last column meets the current token); ``carry`` fp32
+    [slots, row]: a request's last n - 1 inputs live at columns carry_col .. carry_col + (n - 1) C of its row and
+    are replaced by this step's."""
+    for t, n in ((x, "x"), (taps, "taps"), (carry, "carry"), (out, "out")):
+        _check(t, n, torch.float32)
+    _check(seq_of, "seq_of", torch.int32)
+    _check_runs(query_start, slots, S)
+    C, n = taps.shape
+    if x.dim() != 2 or x.shape[0] < T or col + C > x.shape[1] or out.numel() < T * C or carry.dim() != 2 or \
+            carry_col + (n - 1) * C > carry.shape[1] or (bias is not None and bias.numel() != C):
+        raise KernelError(f"conv_silu: {C} channels x {n} taps from column {col} of {tuple(x.shape)}, carry {tuple(carry.shape)}")
+    lib = _lib("recurrent")
+    _call(lib, lib.ember_conv_silu, _p(x), c_int(x.shape[1]), c_int(col), _p(taps), _p(bias), c_int(n), _off(carry, carry_col),
+          c_longlong(carry.shape[1]), _p(seq_of), _p(query_start), _p(slots), _p(out), c_int(T), c_int(S), c_int(C),
+          _stream(stream))
+
+
+def delta_scan(conv: torch.Tensor, beta: torch.Tensor, beta_col: int, a: torch.Tensor, a_col: int, dt_bias: torch.Tensor,
+               A_log: torch.Tensor, state: torch.Tensor, out: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor,
+               S: int, heads: int, kv_heads: int, dim: int, vdim: int, key_eps: float, stream: Optional[int] = None) -> None:
+    """Delta rule with a decay per head and key channel over the step's runs; the state [slots, >= heads dim vdim]
+    fp32 is read and left updated.  ``conv`` fp32 [T, q | k | v] after convolution and silu, ``beta`` logits at
+    column beta_col, decay logits at column a_col of ``a``; out fp32 [T, heads vdim]."""
+    for t, n in ((conv, "conv"), (beta, "beta"), (a, "a"), (dt_bias, "dt_bias"), (A_log, "A_log"), (state, "state"), (out, "out")):
+        _check(t, n, torch.float32)
+    _check_runs(query_start, slots, S)
+    if conv.shape[1] != 2 * kv_heads * dim + heads * vdim or beta_col + heads > beta.shape[1] or \
+            a_col + heads * dim > a.shape[1] or dt_bias.numel() != heads * dim or A_log.numel() != heads or \
+            state.dim() != 2 or state.shape[1] < heads * dim * vdim:
+        raise KernelError("delta_scan: buffers do not fit the head geometry")
+    lib = _lib("recurrent")
+    _call(lib, lib.ember_delta_scan, _p(conv), c_int(conv.shape[1]), _off(beta, beta_col), c_int(beta.shape[1]), _off(a, a_col),
+          c_int(a.shape[1]), _p(dt_bias), _p(A_log), _p(state), c_longlong(state.shape[1]), _p(out), _p(query_start), _p(slots),
+          c_int(S), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_float(key_eps), _stream(stream))
+
+
+def memory_scan(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, off_i: int, off_f: int, bias_i: torch.Tensor,
+                bias_f: torch.Tensor, cap: float, state: torch.Tensor, gates: torch.Tensor, out: torch.Tensor,
+                query_start: torch.Tensor, slots: torch.Tensor, S: int, heads: int, dim: int, vdim: int,
+                stream: Optional[int] = None) -> None:
+    """Matrix memory with exponential input gate and running maximum over the step's runs.  ``proj`` fp32 [T, ld]
+    holds q, k, v and the two gates' logits at the given columns; the state row of a request is S [heads, dim, vdim],
+    n [heads, dim], m [heads]; ``gates`` fp32 scratch [T, heads, 3]; out fp32 [T, heads vdim]."""
+    for t, n in ((proj, "proj"), (bias_i, "bias_i"), (bias_f, "bias_f"), (state, "state"), (gates, "gates"), (out, "out")):
+        _check(t, n, torch.float32)
+    _check_runs(query_start, slots, S)
+    if state.dim() != 2 or state.shape[1] < heads * dim * vdim + heads * dim + heads or bias_i.numel() != heads or \
+            bias_f.numel() != heads:
+        raise KernelError("memory_scan: buffers do not fit the head geometry")
+    lib = _lib("recurrent")
+    _call(lib, lib.ember_memory_scan, _p(proj), c_int(proj.shape[1]), c_int(off_q), c_int(off_k), c_int(off_v), c_int(off_i),
+          c_int(off_f), _p(bias_i), _p(bias_f), c_float(cap), _p(state), c_longlong(state.shape[1]), _p(gates), _p(out),
+          _p(query_start), _p(slots), c_int(S), c_int(heads), c_int(dim), c_int(vdim), _stream(stream))
+
+
+def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, A_log: torch.Tensor, skip: torch.Tensor,
+             state: torch.Tensor, out: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor, S: int, heads: int,
+             groups: int, n_state: int, vdim: int, stream: Optional[int] = None) -> None:
+    """Selective state space with a scalar decay per head over the step's runs.  ``conv`` fp32 [T, x | B | C] after
+    convolution and silu, raw step sizes at column dt_col of ``dt``; state [slots, >= heads n_state vdim] fp32."""
+    for t, n in ((conv, "conv"), (dt, "dt"), (dt_bias, "dt_bias"), (A_log, "A_log"), (skip, "skip"), (state, "state"), (out, "out")):
+        _check(t, n, torch.float32)
+    _check_runs(query_start, slots, S)
+    if conv.shape[1] != heads * vdim + 2 * groups * n_state or dt_col + heads > dt.shape[1] or \
+            state.dim() != 2 or state.shape[1] < heads * n_state * vdim:
+        raise KernelError("ssm_scan: buffers do not fit the head geometry")
+    lib = _lib("recurrent")
+    _call(lib, lib.ember_ssm_scan, _p(conv), c_int(conv.shape[1]), _off(dt, dt_col), c_int(dt.shape[1]), _p(dt_bias), _p(A_log),
+          _p(skip), _p(state), c_longlong(state.shape[1]), _p(out), _p(query_start), _p(slots), c_int(S), c_int(heads),
+          c_int(groups), c_int(n_state), c_int(vdim), _stream(stream))
+
+
+# ------------------------------------------------------- attention without softmax (csrc/sigmoid_attention.cu)
+SIGMOID_ATTENTION_TILE_QUERIES = 16
+
+
+def rotate_store(qkv: torch.Tensor, T: int, heads: int, kv_heads: int, dim: int, vdim: int, inv_freq: Optional[torch.Tensor],
+                 rotary: int, positions: torch.Tensor, seq_of: torch.Tensor, block_table: torch.Tensor, page: int,
+                 k_pool: torch.Tensor, v_pool: torch.Tensor, q_out: torch.Tensor, write_kv: bool = True,
+                 err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """Rotation of query and key heads (first ``rotary`` elements, rotate-half pairs), queries to ``q_out``, keys
+    [.., dim] and values [.., vdim] into their pages.  ``qkv`` is fp32 [T, q | k | v]."""
+    _check(qkv, "qkv", torch.float32)
+    _check(q_out, "q_out")
+    _check(k_pool, "k_pool", q_out.dtype)
+    _check(v_pool, "v_pool", q_out.dtype)
+    for t, n in ((positions, "positions"), (seq_of, "seq_of"), (block_table, "block_table")):
+        _check(t, n, torch.int32)
+    if tuple(k_pool.shape[1:]) != (kv_heads, page, dim) or tuple(v_pool.shape[1:]) != (kv_heads, page, vdim) or \
+            k_pool.shape[0] != v_pool.shape[0]:
+        raise KernelError(f"rotate_store: pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit")
+    if inv_freq is not None:
+        _check(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() * 2 != rotary:
+            raise KernelError(f"rotate_store: {inv_freq.numel()} frequencies for a rotation of {rotary}")
+    if q_out.numel() < T * heads * dim or qkv.shape[0] < T:
+        raise KernelError("rotate_store: buffers too small for the step")
+    lib = _lib("sigmoid_attention")
+    _call(lib, lib.ember_rotate_store, _p(qkv), c_int(qkv.shape[1]), c_int(T), c_int(heads), c_int(kv_heads), c_int(dim),
+          c_int(vdim), _p(inv_freq), c_int(rotary if inv_freq is not None else 0), _p(positions), _p(seq_of), _p(block_table),
+          c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), _p(q_out), _p(k_pool), _p(v_pool),
+          c_int(dtype_code(q_out.dtype)), c_int(1 if write_kv else 0), _p(err), _stream(stream))
+
+
+def sigmoid_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, heads: int,
+                      kv_heads: int, dim: int, vdim: int, tiles: torch.Tensor, n_tiles: int, block_table: torch.Tensor,
+                      page: int, scale: float, head_bias: Optional[torch.Tensor], err: Optional[torch.Tensor] = None,
+                      stream: Optional[int] = None) -> None:
+    """out[t, h] = sum over keys j <= t of sigmoid(scale * q . k_j + head_bias[h]) * v_j (no normalisation)."""
+    _check(q, "q")
+    for t, n in ((out, "out"), (k_pool, "k_pool"), (v_pool, "v_pool")):
+        _check(t, n, q.dtype)
+    _check(tiles, "tiles", torch.int32)
+    _check(block_table, "block_table", torch.int32)
+    if head_bias is not None:
+        _check(head_bias, "head_bias", torch.float32)
+    if tuple(k_pool.shape[1:]) != (kv_heads, page, dim) or tuple(v_pool.shape[1:]) != (kv_heads, page, vdim):
+        raise KernelError(f"sigmoid_attention: pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit")
+    lib = _lib("sigmoid_attention")
+    _call(lib, lib.ember_sigmoid_attention, _p(q), _p(k_pool), _p(v_pool), _p(out), c_int(dtype_code(q.dtype)), c_int(heads),
+          c_int(kv_heads), c_int(dim), c_int(vdim), _p(tiles), c_int(n_tiles), _p(block_table), c_int(block_table.shape[-1]),
+          c_int(page), c_int(k_pool.shape[0]), c_float(scale), _p(head_bias), _p(err), _stream(stream))

@@ -15,6 +15,8 @@ Interfaces (what a new part must provide):
   ``forward(ctx, x[T, hidden], residual_f32[T, hidden], cache: LayerCache | None, owns_cache: bool)``;
   it *adds* its result to ``residual``.
 * ``FeedForward``:   ``forward(ctx, x[T, hidden], residual_f32[T, hidden])``; it adds its result.
+* ``Gate``:          ``forward(ctx, x[T, hidden], logits_f32[T, size])``.
+* Mixers and feed-forwards with ``can_store = True`` also take ``accumulate=False``: the result is stored, not added.
 
 No part knows which model it is in: sizes and constants come from its spec, weights from the
 names under the prefix it is given.  A part whose ``forward`` only launches kernels that read the step's
@@ -24,7 +26,7 @@ every part of it says so.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -37,8 +39,10 @@ class WeightDecl:
 
     name: str
     shape: Tuple[int, ...]
-    init: str = "linear"      # "linear": N(0, std) | "norm": 1 + N(0, norm_std) | "zeros"
+    init: str = "linear"      # "linear": N(0, std) | "norm": 1 + N(0, norm_std) | "zeros" | "uniform": U(lo, hi)
     optional: bool = False    # may be absent from the file (the part then does without)
+    lo: float = 0.0           # bounds of init "uniform"
+    hi: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -55,6 +59,7 @@ class CacheNeed:
     num_kv_heads: int = 0
     head_dim: int = 0
     window: int = 0
+    value_dim: int = 0            # size of a value head where it differs from a key head's (0: the same)
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
 
@@ -146,15 +151,35 @@ class PositionEncoding(Part):
 class Mixer(Part):
     family = "mixer"
 
+    # A mixer that can *store* its result instead of adding it (``forward(..., accumulate=False)``) says so here;
+    # an arrangement that puts something between a mixer and the residual stream hands other mixers a zeroed buffer.
+    can_store = False
+
     def cache_need(self) -> Optional[CacheNeed]:
         return None
+
+    def cache_needs(self) -> Dict[str, Optional[CacheNeed]]:
+        """Needs by sub-id: {"": cache_need()} for an ordinary mixer; a mixer made of several (each with a cache
+        of its own) names them, and its ``forward`` then receives a mapping from those names to caches."""
+        return {"": self.cache_need()}
 
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, cache, owns_cache: bool = True) -> None:
         raise NotImplementedError
 
 
+class Gate(Part):
+    """An element-wise gate on a sublayer's result, computed from the sublayer's input."""
+
+    family = "gate"
+
+    def forward(self, ctx, x: torch.Tensor, logits: torch.Tensor) -> None:
+        """logits[T, size] (fp32) = what the sigmoid is taken of, less the part's ``bias`` (fp32 [size] or None)."""
+        raise NotImplementedError
+
+
 class FeedForward(Part):
     family = "feed_forward"
+    can_store = False
 
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor) -> None:
         raise NotImplementedError

@@ -61,9 +61,22 @@ class Arrangement:
         for p in self.parts.values():
             p.load(store, rt)
 
+    @staticmethod
+    def _join(sub: str, inner: str) -> str:
+        return inner if not sub else (sub if not inner else f"{sub}.{inner}")
+
     def cache_needs(self) -> Dict[str, Optional[CacheNeed]]:
-        """What each mixer of the block asks of the cache manager, by sub-id."""
-        return {sub: m.cache_need() for sub, m in self.mixers.items()}
+        """What each mixer of the block asks of the cache manager, by sub-id.  A mixer made of several mixers
+        (``Mixer.cache_needs`` with names of its own) contributes one entry per inner mixer."""
+        return {self._join(sub, inner): need for sub, m in self.mixers.items() for inner, need in m.cache_needs().items()}
+
+    def cache_of(self, caches: Mapping[str, object], sub: str = ""):
+        """What ``forward`` hands to the mixer with sub-id ``sub``: its cache, or for a mixer made of several a
+        mapping from its inner names to their caches."""
+        inner = list(self.mixers[sub].cache_needs())
+        if inner == [""]:
+            return caches[sub]
+        return {name: caches[self._join(sub, name)] for name in inner}
 
     def tile_requests(self):
         """Attention tile shapes the block's mixers will ask the step context for."""
@@ -90,9 +103,62 @@ class PreNormBlock(Arrangement):
     def forward(self, ctx, h: torch.Tensor, caches, owns_cache: bool = True) -> None:
         x = ctx.buf("block.normed", (ctx.max_tokens, h.shape[-1]), self.rt.dtype)
         self.mixer_norm.forward(ctx, h, x, ctx.T)
-        self.mixer.forward(ctx, x, h, caches[""], owns_cache)
+        self.mixer.forward(ctx, x, h, self.cache_of(caches), owns_cache)
         self.feed_forward_norm.forward(ctx, h, x, ctx.T)
         self.feed_forward.forward(ctx, x, h)
 
 
+class GatedSandwichBlock(Arrangement):
+    """A norm before and after each sublayer, and a gate computed from the sublayer's input on its result:
+
+        x = norm_in(h);  h += norm_out( sublayer(x) * sigmoid(gate(x)) )
+
+    once for the mixer and once for the feed-forward (a layer may have no feed-forward, and either gate may be
+    left out).  The sublayer stores its fp32 result in a buffer (``can_store``; others add into a zeroed one); gate,
+    output norm and the addition to the residual stream are one kernel (the output norm's ``gated_add``)."""
+
+    ROLES = {"mixer_norm": "norm", "mixer": "mixer", "mixer_gate": "gate", "mixer_out_norm": "norm",
+             "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_gate": "gate",
+             "feed_forward_out_norm": "norm"}
+    OPTIONAL = frozenset({"mixer_gate", "feed_forward_norm", "feed_forward", "feed_forward_gate", "feed_forward_out_norm"})
+
+    def __init__(self, layer_spec):
+        super().__init__(layer_spec)
+        p = self.parts
+        if ("feed_forward" in p) != ("feed_forward_norm" in p) or ("feed_forward" in p) != ("feed_forward_out_norm" in p):
+            raise ConfigError("a gated-sandwich layer has a feed-forward with both of its norms, or none of the three")
+        for role in ("mixer_out_norm", "feed_forward_out_norm"):
+            if role in p and not hasattr(p[role], "gated_add"):
+                raise ConfigError(f"the norm in the role {role!r} cannot gate, norm and add in one kernel (no gated_add)")
+
+    def _sublayer(self, ctx, h, x, norm_in, run, gate, norm_out, can_store: bool) -> None:
+        T, hidden = ctx.T, h.shape[-1]
+        y = ctx.buf("block.sublayer", (ctx.max_tokens, hidden), torch.float32)
+        norm_in.forward(ctx, h, x, T)
+        if not can_store:
+            y[:T].zero_()
+        run(y)
+        logits = None
+        if gate is not None:
+            logits = ctx.buf("block.gate", (ctx.max_tokens, hidden), torch.float32)
+            gate.forward(ctx, x, logits)
+        norm_out.gated_add(ctx, y, logits, h, T, gate_bias=getattr(gate, "bias", None))
+
+    def forward(self, ctx, h: torch.Tensor, caches, owns_cache: bool = True) -> None:
+        p = self.parts
+        x = ctx.buf("block.normed", (ctx.max_tokens, h.shape[-1]), self.rt.dtype)
+        mixer = p["mixer"]
+        store = bool(getattr(mixer, "can_store", False))
+        kw = {"accumulate": False} if store else {}
+        self._sublayer(ctx, h, x, p["mixer_norm"], lambda y: mixer.forward(ctx, x, y, self.cache_of(caches), owns_cache, **kw),
+                       p.get("mixer_gate"), p["mixer_out_norm"], store)
+        ff = p.get("feed_forward")
+        if ff is not None:
+            store = bool(getattr(ff, "can_store", False))
+            kw = {"accumulate": False} if store else {}
+            self._sublayer(ctx, h, x, p["feed_forward_norm"], lambda y: ff.forward(ctx, x, y, **kw),
+                           p.get("feed_forward_gate"), p["feed_forward_out_norm"], store)
+
+
 register_part("arrangement", "prenorm", PreNormBlock)
+register_part("arrangement", "gated_sandwich", GatedSandwichBlock)

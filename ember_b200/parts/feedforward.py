@@ -1,4 +1,4 @@
-"""Gated feed-forward (SwiGLU): h += down( silu(gate(x)) * up(x) ), no biases.
+"""Gated feed-forward: h += down( act(gate(x)) * up(x) ), no biases; act = silu (SwiGLU) or relu.
 
 Formula: src/backend/cpu/cpu_backend.cpp:204-211 with silu(g) = g / (1 + exp(-g)).
 Device layout: gate and up rows are interleaved (even rows gate, odd rows up) into one
@@ -20,24 +20,26 @@ from .registry import register_part
 
 class GatedMLP(FeedForward):
     graph_safe = True
+    can_store = True
 
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
-        if spec.activation != "silu":
-            raise ConfigError(f"activation {spec.activation!r} is not supported (silu only)")
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ConfigError(f"activation {spec.activation!r} is not supported ({', '.join(ops.ACTIVATIONS)})")
 
     def weight_decls(self) -> List[WeightDecl]:
         s, p = self.spec, self.prefix
-        return [WeightDecl(p + "gate_proj.weight", (s.intermediate_size, s.hidden_size)),
-                WeightDecl(p + "up_proj.weight", (s.intermediate_size, s.hidden_size)),
-                WeightDecl(p + "down_proj.weight", (s.hidden_size, s.intermediate_size))]
+        g, u, d = s.names
+        return [WeightDecl(p + g, (s.intermediate_size, s.hidden_size)),
+                WeightDecl(p + u, (s.intermediate_size, s.hidden_size)),
+                WeightDecl(p + d, (s.hidden_size, s.intermediate_size))]
 
     def load(self, store, rt: Runtime) -> None:
         s, p = self.spec, self.prefix
         self.rt = rt
-        gate = store.take(p + "gate_proj.weight", (s.intermediate_size, s.hidden_size))
-        up = store.take(p + "up_proj.weight", (s.intermediate_size, s.hidden_size))
-        down = store.take(p + "down_proj.weight", (s.hidden_size, s.intermediate_size))
+        gate = store.take(p + s.names[0], (s.intermediate_size, s.hidden_size))
+        up = store.take(p + s.names[1], (s.intermediate_size, s.hidden_size))
+        down = store.take(p + s.names[2], (s.hidden_size, s.intermediate_size))
         if gate is None or up is None or down is None:
             return
         wd = rt.weight_dtype(torch.result_type(gate, up))
@@ -45,11 +47,17 @@ class GatedMLP(FeedForward):
         self.gate_up = Linear(gu.reshape(2 * s.intermediate_size, s.hidden_size).contiguous())
         self.down = Linear.from_host(down, rt)
 
-    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor) -> None:
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
         s = self.spec
         act = ctx.buf("gated_mlp.act", (ctx.max_tokens, s.intermediate_size), self.rt.dtype)
-        self.gate_up(ctx, x, act, ctx.T, ops.EPI_SILU_MUL)
-        self.down(ctx, act, residual, ctx.T, ops.EPI_ADD_F32)
+        if s.activation == "silu":
+            self.gate_up(ctx, x, act, ctx.T, ops.EPI_SILU_MUL)
+        else:
+            # other activations: the product stores its interleaved (gate, up) pairs and a kernel of its own folds them
+            both = ctx.buf("gated_mlp.gate_up", (ctx.max_tokens, 2 * s.intermediate_size), self.rt.dtype)
+            self.gate_up(ctx, x, both, ctx.T, ops.EPI_STORE)
+            ops.act_mul_interleaved(both, act, s.activation, ctx.T * s.intermediate_size, stream=ctx.stream)
+        self.down(ctx, act, residual, ctx.T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -1,4 +1,4 @@
-"""RMSNorm: out = weight * (x * rsqrt(mean(x^2) + eps)), statistics in fp32.
+"""Norms.  RMSNorm: out = weight * (x * rsqrt(mean(x^2) + eps)), statistics in fp32.
 
 Formula: src/backend/cpu/cpu_backend.cpp:34-39 (the weight multiplies after the scaling; it
 is the plain weight, not 1 + weight).
@@ -31,5 +31,43 @@ class RMSNorm(Norm):
     def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
         ops.rmsnorm(x, self.weight, self.spec.eps, out, n_rows, rows=rows, stream=ctx.stream)
 
+    def gated_add(self, ctx, y: torch.Tensor, gate_logits: Optional[torch.Tensor], residual: torch.Tensor, n_rows: int,
+                  gate_bias: Optional[torch.Tensor] = None) -> None:
+        """residual += norm(y * sigmoid(gate_logits + gate_bias)) in one kernel (no gate if ``gate_logits`` is None)."""
+        ops.gated_norm_add(y, gate_logits, self.weight, None, self.spec.eps, False, residual, n_rows, gate_bias=gate_bias,
+                           stream=ctx.stream)
+
+
+class LayerNorm(Norm):
+    """out = (x - mean) / sqrt(var + eps) * weight + bias, var = mean((x - mean)^2), statistics in fp32."""
+
+    graph_safe = True
+
+    def _names(self):
+        return self.prefix + self.spec.weight_suffix, self.prefix + self.spec.bias_suffix
+
+    def weight_decls(self) -> List[WeightDecl]:
+        w, b = self._names()
+        return [WeightDecl(w, (self.spec.size,), init="norm"), WeightDecl(b, (self.spec.size,), init="zeros")]
+
+    def load(self, store, rt: Runtime) -> None:
+        w, b = (store.take(n, (self.spec.size,)) for n in self._names())
+        self.weight = rt.to_device(w, torch.float32) if w is not None else None
+        self.bias = rt.to_device(b, torch.float32) if b is not None else None
+
+    def scale_output(self, scale: float) -> None:
+        if self.weight is not None:
+            self.weight, self.bias = self.weight * scale, self.bias * scale
+
+    def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
+        ops.layer_norm(x, self.weight, self.bias, self.spec.eps, out, n_rows, rows=rows, stream=ctx.stream)
+
+    def gated_add(self, ctx, y: torch.Tensor, gate_logits: Optional[torch.Tensor], residual: torch.Tensor, n_rows: int,
+                  gate_bias: Optional[torch.Tensor] = None) -> None:
+        """residual += norm(y * sigmoid(gate_logits + gate_bias)) in one kernel (no gate if ``gate_logits`` is None)."""
+        ops.gated_norm_add(y, gate_logits, self.weight, self.bias, self.spec.eps, True, residual, n_rows, gate_bias=gate_bias,
+                           stream=ctx.stream)
+
 
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

@@ -28,6 +28,8 @@ class RotaryEmbedding(PositionEncoding):
 
     def inv_freq(self) -> np.ndarray:
         r = self.spec.rotary_dim
+        if getattr(self.spec, "frequency_precision", "float32") == "float64":
+            return np.power(float(self.spec.theta), -2.0 * np.arange(r // 2, dtype=np.float64) / r).astype(np.float32)
         i = np.arange(r // 2, dtype=np.float32)
         exponent = (np.float32(2.0) * i) / np.float32(r)                      # float(2i) / float(D)
         return (np.float32(1.0) / np.power(np.float32(self.spec.theta), exponent, dtype=np.float32)).astype(np.float32)
@@ -38,7 +40,7 @@ class RotaryEmbedding(PositionEncoding):
         return self._table, self.spec.rotary_dim
 
     def table_key(self):
-        return (self.spec.rotary_dim, float(self.spec.theta))        # equal frequencies: one table a step
+        return (self.spec.rotary_dim, float(self.spec.theta), getattr(self.spec, "frequency_precision", "float32"))
 
 
 class NoPosition(PositionEncoding):

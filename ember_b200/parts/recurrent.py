@@ -1,0 +1,254 @@
+"""Mixers whose memory is a fixed-size state per request (kept in the request's state slot, fp32):
+
+* "channel_delta": delta-rule memory with a decay per head and key channel,
+* "mlstm":         matrix memory with an exponential input gate and a running maximum,
+* "mamba2":        selective state space with a scalar decay per head.
+
+All three project their input with one fused product whose fp32 result the recurrence kernel reads in place (column
+offsets, no copies), run the same kernels for prompt portions and single tokens (a block walks its run's tokens in
+order, so the state after a step does not depend on how the tokens were cut), normalise each head's read-out in
+fp32 and end in an output product that stores into, or adds into, an fp32 [T, hidden] buffer.  A short causal
+convolution's last inputs are part of the state.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .. import ops
+from ..config.spec import ConfigError
+from .base import CacheNeed, Mixer, Runtime, WeightDecl
+from .linear import Linear
+from .registry import register_part
+
+
+class _StateMixer(Mixer):
+    graph_safe = True
+    can_store = True
+
+    def state_floats(self) -> int:
+        raise NotImplementedError
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kind="state", state_shape=(self.state_floats(),), state_dtype="float32")
+
+    def _take_all(self, store):
+        got = {d.name: store.take(d.name, d.shape) for d in self.weight_decls()}
+        return None if any(v is None for v in got.values()) else got
+
+    def _fused(self, tensors, rt: Runtime) -> Linear:
+        """One matrix from several stored ones (rows concatenated), in the product's dtype."""
+        wd = rt.weight_dtype(tensors[0].dtype)
+        return Linear(torch.cat([rt.to_device(t, wd) for t in tensors], dim=0).contiguous())
+
+    def _out(self, ctx, y, out, accumulate):
+        self.o(ctx, y, out, ctx.T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
+
+
+# --------------------------------------------------------------------------------------- channel_delta
+class GatedDelta(_StateMixer):
+    """Per value head h (query/key head h // (heads / kv_heads)), with unit vectors q (also times dim^-1/2) and k,
+    beta = sigmoid(W_b x), and g = exp(-exp(A_log[h]) * softplus(W_a2 W_a1 x + dt_bias)) per key channel:
+
+        S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+
+    then o / rms(o) * norm * sigmoid(W_g2 W_g1 x) and the output product.  q, k, v each pass a short causal
+    convolution and silu first.  Tensors under the prefix: q, k, v (+ ``.conv``), b, a1, a2, dt_bias, A_log, g1, g2,
+    norm, o."""
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        s = spec
+        if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
+            raise ConfigError(f"{s.num_heads} value heads do not divide into {s.num_kv_heads} query/key heads")
+        if min(s.head_dim, s.value_dim, s.conv_taps) <= 0:
+            raise ConfigError("channel_delta: head sizes and convolution taps must be positive")
+        self.qk, self.vd = s.num_kv_heads * s.head_dim, s.num_heads * s.value_dim
+        self.channels = 2 * self.qk + self.vd
+        self.decay_rank, self.gate_rank = s.decay_rank, s.gate_rank
+
+    def state_floats(self) -> int:
+        s = self.spec
+        return s.num_heads * s.head_dim * s.value_dim + (s.conv_taps - 1) * self.channels
+
+    def weight_decls(self) -> List[WeightDecl]:
+        s, p = self.spec, self.prefix
+        H, D, hid, ra, rg = s.num_heads, s.head_dim, s.hidden_size, self.decay_rank, self.gate_rank
+        if ra <= 0 or rg <= 0:
+            raise ConfigError("channel_delta: the ranks of the decay and gate projections are read from the weights at "
+                              "load; a configuration that lists tensors without a file must give them")
+        return [WeightDecl(p + "q", (self.qk, hid)), WeightDecl(p + "q.conv", (self.qk, s.conv_taps), init="uniform", lo=-0.5, hi=0.5),
+                WeightDecl(p + "k", (self.qk, hid)), WeightDecl(p + "k.conv", (self.qk, s.conv_taps), init="uniform", lo=-0.5, hi=0.5),
+                WeightDecl(p + "v", (self.vd, hid)), WeightDecl(p + "v.conv", (self.vd, s.conv_taps), init="uniform", lo=-0.5, hi=0.5),
+                WeightDecl(p + "b", (H, hid)), WeightDecl(p + "A_log", (H,), init="uniform", lo=-1.0, hi=1.0),
+                WeightDecl(p + "norm", (s.value_dim,), init="norm"),
+                WeightDecl(p + "a1", (ra, hid)), WeightDecl(p + "a2", (H * D, ra)),
+                WeightDecl(p + "dt_bias", (H * D,), init="uniform", lo=-3.0, hi=0.0),
+                WeightDecl(p + "g1", (rg, hid)), WeightDecl(p + "g2", (self.vd, rg)), WeightDecl(p + "o", (hid, self.vd))]
+
+    def load(self, store, rt: Runtime) -> None:
+        s, p = self.spec, self.prefix
+        self.rt = rt
+        for attr, name in (("decay_rank", "a1"), ("gate_rank", "g1")):
+            if getattr(self, attr) <= 0:                   # a size the configuration leaves to the weights
+                shape = store.shape(p + name)
+                setattr(self, attr, int(shape[0]) if shape and len(shape) == 2 else 1)
+        w = self._take_all(store)
+        if w is None:
+            return
+        ra, rg, HD = self.decay_rank, self.gate_rank, s.num_heads * s.head_dim
+        self.in_proj = self._fused([w[p + "q"], w[p + "k"], w[p + "v"], w[p + "b"]], rt)            # [q | k | v | beta]
+        self.low = self._fused([w[p + "a1"], w[p + "g1"]], rt)                                       # [a1 | g1]
+        wd = self.low.weight.dtype
+        up = torch.zeros(HD + self.vd, ra + rg, dtype=wd, device=rt.device)                          # block diagonal
+        up[:HD, :ra] = rt.to_device(w[p + "a2"], wd)
+        up[HD:, ra:] = rt.to_device(w[p + "g2"], wd)
+        self.up = Linear(up)
+        self.o = Linear.from_host(w[p + "o"], rt)
+        self.taps = torch.cat([rt.to_device(w[p + n + ".conv"], torch.float32) for n in "qkv"], dim=0).contiguous()
+        self.dt_bias, self.A_log, self.norm_w = (rt.to_device(w[p + n], torch.float32) for n in ("dt_bias", "A_log", "norm"))
+
+    def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
+        s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
+        H, D, V, C = s.num_heads, s.head_dim, s.value_dim, self.channels
+        proj = ctx.buf("delta.proj", (mt, C + H), torch.float32)
+        low = ctx.buf("delta.low", (mt, self.decay_rank + self.gate_rank), rt.dtype)
+        ag = ctx.buf("delta.decay_gate", (mt, H * D + self.vd), torch.float32)
+        conv = ctx.buf("delta.conv", (mt, C), torch.float32)
+        o = ctx.buf("delta.read", (mt, self.vd), torch.float32)
+        y = ctx.buf("delta.normed", (mt, self.vd), rt.dtype)
+        self.in_proj(ctx, x, proj, T, ops.EPI_STORE_F32)
+        self.low(ctx, x, low, T, ops.EPI_STORE)
+        self.up(ctx, low, ag, T, ops.EPI_STORE_F32)
+        ops.conv_silu(proj, 0, self.taps, None, cache.state, H * D * V, ctx.seq_of, ctx.query_start, ctx.state_slots, conv,
+                      T, ctx.S, stream=ctx.stream)
+        ops.delta_scan(conv, proj, C, ag, 0, self.dt_bias, self.A_log, cache.state, o, ctx.query_start, ctx.state_slots,
+                       ctx.S, H, s.num_kv_heads, D, V, s.key_eps, stream=ctx.stream)
+        ops.group_norm_gate(o, 0, ag, H * D, self.norm_w, False, s.norm_eps, ops.GATE_SIGMOID_AFTER, y, T, H, V,
+                            stream=ctx.stream)
+        self._out(ctx, y, out, accumulate)
+
+
+# ----------------------------------------------------------------------------------------------- mlstm
+class MatrixMemory(_StateMixer):
+    """Per head, with q = W_q x * dim^-1/2, log gates i~ = cap tanh((W_i x + b_i) / cap) and
+    f~ = logsigmoid(cap tanh((W_f x + b_f) / cap)) and a running maximum m that starts at 0:
+
+        m' = max(f~ + m, i~);  S <- e^(f~ + m - m') S + e^(i~ - m') k v^T;  n likewise with k alone
+        o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)
+
+    then o / rms(o) per head, times norm (all heads' size), times sigmoid(W_g x), and the output product.
+    Tensors under the prefix: q, k, v, g, o, norm, i, i.b, f, f.b."""
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        s = spec
+        if min(s.num_heads, s.head_dim, s.value_dim) <= 0 or not s.gate_cap > 0:
+            raise ConfigError("mlstm: head count, sizes and the gate cap must be positive")
+        self.qk, self.vd = s.num_heads * s.head_dim, s.num_heads * s.value_dim
+
+    def state_floats(self) -> int:
+        s = self.spec
+        return s.num_heads * (s.head_dim * s.value_dim + s.head_dim + 1)
+
+    def weight_decls(self) -> List[WeightDecl]:
+        s, p = self.spec, self.prefix
+        H, hid = s.num_heads, s.hidden_size
+        return [WeightDecl(p + "q", (self.qk, hid)), WeightDecl(p + "k", (self.qk, hid)), WeightDecl(p + "v", (self.vd, hid)),
+                WeightDecl(p + "g", (self.vd, hid)), WeightDecl(p + "o", (hid, self.vd)),
+                WeightDecl(p + "norm", (self.vd,), init="norm"),
+                WeightDecl(p + "i", (H, hid)), WeightDecl(p + "i.b", (H,), init="uniform", lo=-1.0, hi=1.0),
+                WeightDecl(p + "f", (H, hid)), WeightDecl(p + "f.b", (H,), init="uniform", lo=1.0, hi=4.0)]
+
+    def load(self, store, rt: Runtime) -> None:
+        p = self.prefix
+        self.rt = rt
+        w = self._take_all(store)
+        if w is None:
+            return
+        self.in_proj = self._fused([w[p + n] for n in ("q", "k", "v", "g", "i", "f")], rt)
+        self.o = Linear.from_host(w[p + "o"], rt)
+        self.bias_i, self.bias_f, self.norm_w = (rt.to_device(w[p + n], torch.float32) for n in ("i.b", "f.b", "norm"))
+
+    def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
+        s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
+        H, D, V = s.num_heads, s.head_dim, s.value_dim
+        off_k, off_v, off_g = self.qk, 2 * self.qk, 2 * self.qk + self.vd
+        off_i = off_g + self.vd
+        proj = ctx.buf("mlstm.proj", (mt, off_i + 2 * H), torch.float32)
+        gates = ctx.buf("mlstm.gates", (mt, H, 3), torch.float32)
+        o = ctx.buf("mlstm.read", (mt, self.vd), torch.float32)
+        y = ctx.buf("mlstm.normed", (mt, self.vd), rt.dtype)
+        self.in_proj(ctx, x, proj, T, ops.EPI_STORE_F32)
+        ops.memory_scan(proj, 0, off_k, off_v, off_i, off_i + H, self.bias_i, self.bias_f, s.gate_cap, cache.state, gates, o,
+                        ctx.query_start, ctx.state_slots, ctx.S, H, D, V, stream=ctx.stream)
+        ops.group_norm_gate(o, 0, proj, off_g, self.norm_w, True, s.norm_eps, ops.GATE_SIGMOID_AFTER, y, T, H, V,
+                            stream=ctx.stream)
+        self._out(ctx, y, out, accumulate)
+
+
+# ---------------------------------------------------------------------------------------------- mamba2
+class StateSpace(_StateMixer):
+    """W_in x = [z | x | B | C | dt]; x, B, C pass a short causal convolution (with bias) and silu;
+    dt = softplus(dt + dt_bias); per head h (B, C of group h // (heads / groups)):
+
+        S <- exp(-exp(A_log[h]) dt) S + dt B x^T  (S is state x vdim);  y = S^T C + D[h] x
+
+    then y * silu(z), an RMS norm in ``norm_groups`` equal parts times norm, and the output product.
+    Tensors under the prefix: in, conv, conv.b, dt_bias, A_log, D, norm, o."""
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        s = spec
+        if min(s.num_heads, s.value_dim, s.state_size, s.num_groups, s.norm_groups, s.conv_taps) <= 0:
+            raise ConfigError("mamba2: sizes must be positive")
+        if s.num_heads % s.num_groups or s.inner % s.norm_groups:
+            raise ConfigError(f"mamba2: {s.num_heads} heads in {s.num_groups} groups, {s.inner} channels in {s.norm_groups} norm groups")
+        self.channels = s.inner + 2 * s.num_groups * s.state_size
+
+    def state_floats(self) -> int:
+        s = self.spec
+        return s.num_heads * s.state_size * s.value_dim + (s.conv_taps - 1) * self.channels
+
+    def weight_decls(self) -> List[WeightDecl]:
+        s, p = self.spec, self.prefix
+        H, hid = s.num_heads, s.hidden_size
+        return [WeightDecl(p + "in", (s.inner + self.channels + H, hid)),
+                WeightDecl(p + "conv", (self.channels, s.conv_taps), init="uniform", lo=-0.5, hi=0.5),
+                WeightDecl(p + "conv.b", (self.channels,), init="zeros"),
+                WeightDecl(p + "dt_bias", (H,), init="uniform", lo=-3.0, hi=-1.0),
+                WeightDecl(p + "A_log", (H,), init="uniform", lo=0.0, hi=2.0), WeightDecl(p + "D", (H,), init="norm"),
+                WeightDecl(p + "norm", (s.inner,), init="norm"), WeightDecl(p + "o", (hid, s.inner))]
+
+    def load(self, store, rt: Runtime) -> None:
+        p = self.prefix
+        self.rt = rt
+        w = self._take_all(store)
+        if w is None:
+            return
+        self.in_proj = Linear.from_host(w[p + "in"], rt)
+        self.o = Linear.from_host(w[p + "o"], rt)
+        self.taps, self.conv_bias, self.dt_bias, self.A_log, self.skip, self.norm_w = (
+            rt.to_device(w[p + n], torch.float32) for n in ("conv", "conv.b", "dt_bias", "A_log", "D", "norm"))
+
+    def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
+        s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
+        H, V, N, inner, C = s.num_heads, s.value_dim, s.state_size, s.inner, self.channels
+        proj = ctx.buf("mamba2.proj", (mt, inner + C + H), torch.float32)
+        conv = ctx.buf("mamba2.conv", (mt, C), torch.float32)
+        o = ctx.buf("mamba2.read", (mt, inner), torch.float32)
+        y = ctx.buf("mamba2.normed", (mt, inner), rt.dtype)
+        self.in_proj(ctx, x, proj, T, ops.EPI_STORE_F32)
+        ops.conv_silu(proj, inner, self.taps, self.conv_bias, cache.state, H * N * V, ctx.seq_of, ctx.query_start,
+                      ctx.state_slots, conv, T, ctx.S, stream=ctx.stream)
+        ops.ssm_scan(conv, proj, inner + C, self.dt_bias, self.A_log, self.skip, cache.state, o, ctx.query_start,
+                     ctx.state_slots, ctx.S, H, s.num_groups, N, V, stream=ctx.stream)
+        ops.group_norm_gate(o, 0, proj, 0, self.norm_w, True, s.norm_eps, ops.GATE_SILU_BEFORE, y, T, s.norm_groups,
+                            inner // s.norm_groups, stream=ctx.stream)
+        self._out(ctx, y, out, accumulate)
+
+
+register_part("mixer", "channel_delta", GatedDelta)
+register_part("mixer", "mlstm", MatrixMemory)
+register_part("mixer", "mamba2", StateSpace)

@@ -112,6 +112,11 @@ class WeightStore:
     def has(self, name: str) -> bool:
         return self._src.has(name)
 
+    def shape(self, name: str) -> Optional[Tuple[int, ...]]:
+        """The stored shape of ``name``, or None if the source has no such tensor (a part may read a size that the
+        configuration leaves to the weights from here)."""
+        return tuple(self._src.shape(name)) if self._src.has(name) else None
+
     def allow_unused(self, pattern: str) -> None:
         """Names matching ``pattern`` (fnmatch) may be present without being used."""
         self._ignored_patterns.append(pattern)

@@ -55,6 +55,8 @@ class RandomSource:
         t = torch.empty(d.shape, dtype=torch.float32, device=self.device)
         if d.init == "norm":
             t.normal_(0.0, self.norm_std, generator=g).add_(1.0)
+        elif d.init == "uniform":
+            t.uniform_(d.lo, d.hi, generator=g)
         else:                                   # matrices, and biases ("zeros" names what a trained model often has)
             t.normal_(0.0, self.std, generator=g)
         return t.to(self._dtype)
