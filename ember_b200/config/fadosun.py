@@ -63,7 +63,10 @@ class FadosunConfig:
                   eps=_float(_need(config, "norm", "the model"), "eps", "norm"),
                   layers=tuple(copy.deepcopy(dict(l)) for l in layers),
                   max_positions=int(config.get("max_positions") or (1 << 20)))
-        out.to_model_spec()                 # every layer's keys are read (and refused) now, not at the first step
+        # every layer's keys are read and every part is built (without a device) now, so that a bad value is
+        # refused here and not at the first step
+        from ..model.causal_lm import CausalLM
+        CausalLM(out.to_model_spec())
         return out
 
     # ------------------------------------------------------------------ mixers
