@@ -18,6 +18,7 @@ Other workloads of the same engine, one JSON line each (not part of the default 
 
     python bench.py --workload serving-8b    # Qwen3-8B shape: 64 requests, prompts U[128, 2048], 512-token portions, 256 tokens each
     python bench.py --workload qwen3-32b     # Qwen3-32B shape: 2,048-token prefill, decode at batch 1 and 8 to 4,096, cache from free memory
+    python bench.py --workload fadosun [--breakdown]   # Fadosun beside Qwen3 at equal width, feed-forward and layers
 """
 from __future__ import annotations
 
@@ -145,7 +146,8 @@ def fill_cache(llm, batch, context):
     import torch
     r = llm.runner
     for t in r.storage._paged.values():
-        t.normal_(0.0, 0.5)
+        for x in (t if isinstance(t, tuple) else (t,)):
+            x.normal_(0.0, 0.5)
     ids = []
     for i in range(batch):
         rid = ("bench", i)
@@ -322,6 +324,117 @@ def breakdown(cfg, n_layers, batch) -> int:
     return 0
 
 
+FADOSUN_LAYERS = [
+    {"type": "channel_delta", "mixer": {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64,
+                                        "gate_rank": 64}},
+    {"type": "parallel", "mixer": {
+        "left": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 0.0884, "rot": {"dims": 64, "base": 1e6}},
+        "right": {"heads": 32, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4},
+        "left_scale": 1.0, "right_scale": 1.0}},
+    {"type": "mlstm", "mixer": {"heads": 8, "dim": 128, "vdim": 256, "gate_cap": 15.0}},
+    {"type": "channel_delta", "mixer": {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64,
+                                        "gate_rank": 64}},
+]
+
+
+def workload_fadosun(args, pk) -> int:
+    """Fadosun beside Qwen3 at equal width, feed-forward, vocabulary and number of layers (the 1.7B widths, 8 layers
+    unless --layers says otherwise; random weights): prefill of 512 and 2,048 tokens and decode steps at batch 8 and 64
+    from a context of 1,024; with --breakdown instead the device time per kernel of one 2,048-token prefill and of a
+    decode step at batch 64 (kernels serialised: no programmatic dependent launch, no graphs)."""
+    import torch
+    import ember_b200
+    from ember_b200 import ops
+    from ember_b200.config import FadosunConfig, Qwen3Config
+    if args.breakdown:
+        os.environ["EMBER_PDL"] = "0"          # kernels one after the other: each one's own time
+    n_layers = args.layers or 8
+    width, ff, vocab = QWEN3_1P7B["hidden_size"], QWEN3_1P7B["intermediate_size"], QWEN3_1P7B["vocab_size"]
+    context, warmup = 1024, max(3, args.warmup)
+    fcfg = FadosunConfig.from_json({"architecture": "Fadosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+                                    "layers": [dict(FADOSUN_LAYERS[i % 4], mlp={"kind": "dense", "ff": ff}) for i in range(n_layers)]})
+    qcfg = Qwen3Config.from_json(dict(QWEN3_1P7B, num_hidden_layers=n_layers))
+
+    def build(cfg, batch):
+        return ember_b200.load_random(cfg, seed=0, dtype="bfloat16", kv_cache_tokens=max(batch * (context + 512), 2048),
+                                      page_tokens=PAGE_TOKENS, max_batch_tokens=2048, max_seqs=max(batch, 1), prefill_chunk=2048)
+
+    def kernel_table(llm, batch):
+        """us per kernel name for one 2,048-token prefill and for a decode step at ``batch`` (kernels serialised)."""
+        from torch.profiler import ProfilerActivity, profile
+        from ember_b200 import StepEntry
+        import random
+        r = llm.runner
+        r.cuda_graphs = False
+        rng = random.Random(1)
+        toks = [rng.randrange(1000, 100000) for _ in range(2048)]
+        out = {}
+
+        def prefill(i):
+            rid = ("kp", i)
+            assert r.admit(rid) and r.reserve(rid, 2048)
+            r.step([StepEntry(rid, toks, (2047,))])
+            torch.cuda.synchronize()
+            r.release(rid)
+
+        def rows(prof, steps):
+            t = {}
+            for e in prof.key_averages():
+                if e.self_device_time_total > 0:
+                    name = e.key.split("(")[0].split("<")[0].split("::")[-1][-48:]
+                    t[name] = t.get(name, 0.0) + e.self_device_time_total / steps
+            return {k: round(v, 1) for k, v in sorted(t.items(), key=lambda x: -x[1])[:14]}
+
+        for i in range(2):
+            prefill(i)
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            prefill(2)
+        out["prefill_2048_us"] = rows(prof, 1)
+        ids = fill_cache(llm, batch, context)
+
+        def decode():
+            for rid in ids:
+                assert r.reserve(rid, 1)
+            r.step([StepEntry(rid, [rng.randrange(1000, 100000)], (0,)) for rid in ids])
+
+        for _ in range(3):
+            decode()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                decode()
+            torch.cuda.synchronize()
+        out[f"decode_b{batch}_us"] = rows(prof, 3)
+        for rid in ids:
+            r.release(rid)
+        return out
+
+    result = {"workload": "fadosun", "layers": n_layers, "width": width, "ff": ff, "vocab": vocab, "dtype": "bf16",
+              "data": "synthetic (random weights from a seed, random token ids)", "decode_from": context,
+              "page_tokens": PAGE_TOKENS, "fadosun_layers": [l["type"] for l in FADOSUN_LAYERS], "peaks": pk["source"]}
+    with ClockSampler() as clocks:
+        for name, cfg in (("fadosun", fcfg), ("qwen3", qcfg)):
+            res = {}
+            llm = build(cfg, 64)
+            if args.breakdown:
+                res["kernels"] = kernel_table(llm, 64)
+            for n_tok in (() if args.breakdown else (512, 2048)):
+                pms = time_prefill(llm, n_tok, reps=3, warmup=2)
+                res[f"prefill_{n_tok}"] = {"ms": round(pms, 3), "tokens_per_s": round(n_tok / (pms * 1e-3), 1)}
+            for batch in (() if args.breakdown else (8, 64)):
+                steps = max(8, args.steps // (1 if batch == 8 else 2))
+                ms, launches, _, _ = time_decode(llm, batch, steps, warmup, context, min_total_ms=300.0, max_steps=400)
+                res[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch * 1000.0 / ms, 1),
+                                           "launches_per_step": round(launches, 1)}
+            result[name] = res
+            del llm
+            torch.cuda.empty_cache()
+    result["clocks"] = clocks.summary()
+    result["gpu_launches"] = ops.launch_count()
+    print(json.dumps(result))
+    return 0
+
+
 def workload_serving_8b(args, pk) -> int:
     """BASELINE's fourth configuration: the Qwen3-8B shape, 64 requests with random-id prompts of lengths uniform in
     [128, 2048], continuous batching with 512-token prompt portions, 256 decoded tokens each, through ``Engine``
@@ -468,9 +581,10 @@ def main() -> int:
                     help="profiling aid: device time per kernel of three decode steps and one 2,048-token prefill step "
                          "(kernels serialised: EMBER_PDL=0 and no CUDA graphs are set by this flag)")
     ap.add_argument("--page-tokens", type=int, default=PAGE_TOKENS, choices=[16, 32, 64], help="tokens per cache page")
-    ap.add_argument("--workload", default="default", choices=["default", "serving-8b", "qwen3-32b"],
-                    help="default: the Qwen3-1.7B line the contract asks for; the others are BASELINE's fourth and fifth "
-                         "configurations, one JSON line each")
+    ap.add_argument("--workload", default="default", choices=["default", "serving-8b", "qwen3-32b", "fadosun"],
+                    help="default: the Qwen3-1.7B line the contract asks for; serving-8b and qwen3-32b are BASELINE's fourth "
+                         "and fifth configurations; fadosun: that design beside Qwen3 at equal sizes (with --breakdown "
+                         "also per kernel); one JSON line each")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only-prefill: another prompt length (the reported line stays at 2,048)")
     ap.add_argument("--decode-from", type=int, default=DECODE_FROM,
@@ -511,6 +625,8 @@ def main() -> int:
         return workload_serving_8b(args, pk)
     if args.workload == "qwen3-32b":
         return workload_qwen3_32b(args, pk)
+    if args.workload == "fadosun":
+        return workload_fadosun(args, pk)
     if args.breakdown:
         return breakdown(cfg, n_layers, args.batch)
     if args.only_prefill:

@@ -76,7 +76,7 @@ gated_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ gat
 template <typename TO>
 __global__ void group_norm_gate_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gate, int ldg,
                                        const float* __restrict__ w, int w_stride, float eps, int gate_mode,
-                                       TO* __restrict__ out, int T, int groups, int V) {
+                                       const float* __restrict__ den4, TO* __restrict__ out, int T, int groups, int V) {
     pdl_launch_dependents();
     pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -84,9 +84,12 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ x, int ldx, con
     const int t = warp / groups, g = warp - t * groups;
     const float* in = x + (size_t)t * ldx + (size_t)g * V;
     const float* gl = gate ? gate + (size_t)t * ldg + (size_t)g * V : nullptr;
+    // den4 (nullable): per (token, group) four floats whose last two are (floor, dot): the group is first divided by
+    // max(|dot|, floor) + 1e-6 (the denominator of a matrix memory's read-out)
+    const float inv = den4 ? 1.0f / (fmaxf(fabsf(den4[(size_t)warp * 4 + 3]), den4[(size_t)warp * 4 + 2]) + 1e-6f) : 1.0f;
     float ss = 0.0f;
     for (int j = lane; j < V; j += 32) {
-        float v = in[j];
+        float v = in[j] * inv;
         if (gate_mode == 2) { const float z = gl[j]; v *= z * sigmoidf_(z); }
         ss = fmaf(v, v, ss);
     }
@@ -94,7 +97,7 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ x, int ldx, con
     TO* o = out + ((size_t)t * groups + g) * V;
     const float* wg = w + (size_t)g * w_stride;
     for (int j = lane; j < V; j += 32) {
-        float v = in[j];
+        float v = in[j] * inv;
         if (gate_mode == 2) { const float z = gl[j]; v *= z * sigmoidf_(z); }
         v = v * r * wg[j];
         if (gate_mode == 1) v *= sigmoidf_(gl[j]);
@@ -157,7 +160,8 @@ EMBER_API int ember_gated_norm_add(const float* y, const float* gate, const floa
 }
 
 EMBER_API int ember_group_norm_gate(const float* x, int ldx, const float* gate, int ldg, const float* w, int w_stride,
-                                    float eps, int gate_mode, void* out, int out_dtype, int T, int groups, int V, void* stream) {
+                                    float eps, int gate_mode, const float* den4, void* out, int out_dtype, int T, int groups, int V,
+                                    void* stream) {
     if (T <= 0) return 0;
     if (groups <= 0 || V <= 0 || ldx < groups * V) return fail("group_norm_gate: %d groups of %d in rows of %d", groups, V, ldx);
     if (gate_mode < 0 || gate_mode > 2 || (gate_mode && (!gate || ldg < groups * V))) return fail("group_norm_gate: bad gate");
@@ -165,10 +169,10 @@ EMBER_API int ember_group_norm_gate(const float* x, int ldx, const float* gate, 
     const long long warps = (long long)T * groups;
     const unsigned blocks = (unsigned)((warps + 7) / 8);
     if (out_dtype == EMBER_F32)
-        launch_kernel(group_norm_gate_kernel<float>, blocks, 256, 0, st, x, ldx, gate, ldg, w, w_stride, eps, gate_mode, (float*)out, T, groups, V);
+        launch_kernel(group_norm_gate_kernel<float>, blocks, 256, 0, st, x, ldx, gate, ldg, w, w_stride, eps, gate_mode, den4, (float*)out, T, groups, V);
     else if (out_dtype == EMBER_BF16)
         launch_kernel(group_norm_gate_kernel<__nv_bfloat16>, blocks, 256, 0, st, x, ldx, gate, ldg, w, w_stride, eps, gate_mode,
-                      (__nv_bfloat16*)out, T, groups, V);
+                      den4, (__nv_bfloat16*)out, T, groups, V);
     else
         return fail("group_norm_gate: unsupported output dtype %d", out_dtype);
     return check_launch("group_norm_gate");

@@ -56,14 +56,21 @@ __global__ void conv_carry_kernel(const float* __restrict__ x, int ldx, int c0, 
 
 // ------------------------------------------------------------------------------------------- state tiles
 // Shared memory of a recurrence block: the state tile [D][VT] (VT = blockDim.x columns), then vectors.
-__device__ __forceinline__ void load_tile(float* tile, const float* __restrict__ S, int D, int V, int j, bool live) {
+// (`extra`, where given, is one more column, number V, kept apart from the matrix: D contiguous floats)
+__device__ __forceinline__ void load_tile(float* tile, const float* __restrict__ S, int D, int V, int j, bool live,
+                                          const float* __restrict__ extra = nullptr) {
     const int VT = blockDim.x;
-    for (int i = 0; i < D; i++) tile[i * VT + threadIdx.x] = live ? S[(size_t)i * V + j] : 0.0f;
+    for (int i = 0; i < D; i++)
+        tile[i * VT + threadIdx.x] = !live ? 0.0f : (j < V ? S[(size_t)i * V + j] : extra[i]);
 }
-__device__ __forceinline__ void store_tile(const float* tile, float* __restrict__ S, int D, int V, int j, bool live) {
+__device__ __forceinline__ void store_tile(const float* tile, float* __restrict__ S, int D, int V, int j, bool live,
+                                           float* __restrict__ extra = nullptr) {
     const int VT = blockDim.x;
     if (live)
-        for (int i = 0; i < D; i++) S[(size_t)i * V + j] = tile[i * VT + threadIdx.x];
+        for (int i = 0; i < D; i++) {
+            if (j < V) S[(size_t)i * V + j] = tile[i * VT + threadIdx.x];
+            else extra[i] = tile[i * VT + threadIdx.x];
+        }
 }
 
 // ---------------------------------------------------------------------- delta rule, one decay per key channel
@@ -143,56 +150,55 @@ __global__ void delta_scan_kernel(DeltaArgs p) {
 // maximum m (0 for a new request):
 //   m' = max(f~ + m, i~);  S <- e^(f~ + m - m') S + e^(i~ - m') k v^T;  n likewise with k;
 //   o = S^T q / (max(|n . q|, e^(-m')) + 1e-6),  q scaled by D^-1/2.
-// Two kernels: the first walks a run once per head and leaves (keep, put, denominator) per token, carrying n and m;
-// the second applies them to the tiles of S.
+// n is the matrix's column number V (its "value" is 1), so n . q is that column's read-out.  Two kernels: the first
+// runs the scalar recurrence of m, one warp per (run, head), 32 tokens at a time as a prefix scan over the pairs
+// (f~, i~) under (a2, b2) o (a1, b1) = (a1 + a2, max(b1 + a2, b2)), and leaves (keep, put, e^-m') per token; the
+// second applies them to the columns and leaves S^T q and n . q; the division is the normalising kernel's.
 struct MemoryArgs {
     const float* proj; int ld;             // [T, ...]: q, k (H D each), v (H V), input and forget logits (H each)
     int off_q, off_k, off_v, off_i, off_f;
     const float* bias_i; const float* bias_f;   // [H]
     float cap;
     float* state; long long state_stride;  // [slot]: S [H][D][V], then n [H][D], then m [H]
-    float* gates;                          // [T, H, 3]: keep, put, denominator
-    float* out;                            // [T, H V]
+    float* gates;                          // [T, H, 4]: keep, put, e^-m', n . q
+    float* out;                            // [T, H V]: S^T q
     const int* query_start; const int* slots;
     int H, D, V;
 };
 
 __global__ void memory_gates_kernel(MemoryArgs p) {
-    extern __shared__ float smem[];           // n [D]
-    __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
-    const int s = blockIdx.x, h = blockIdx.y, D = p.D, H = p.H;
-    float* base = p.state + (size_t)p.slots[s] * p.state_stride + (size_t)H * D * p.V;
-    float* nst = base + (size_t)h * D;
-    float* mst = base + (size_t)H * D + h;
+    const int s = blockIdx.x, h = blockIdx.y, H = p.H, lane = threadIdx.x;
+    float* mst = p.state + (size_t)p.slots[s] * p.state_stride + (size_t)H * p.D * p.V + (size_t)H * p.D + h;
     const int first = p.query_start[s], end = p.query_start[s + 1];
-    for (int i = threadIdx.x; i < D; i += blockDim.x) smem[i] = nst[i];
-    float m = *mst;
-    const float qscale = 1.0f / sqrtf((float)D);
-    for (int t = first; t < end; t++) {
-        const float* row = p.proj + (size_t)t * p.ld;
-        const float ig = p.cap * tanhf((row[p.off_i + h] + p.bias_i[h]) / p.cap);
-        const float fg = logsigmoidf_(p.cap * tanhf((row[p.off_f + h] + p.bias_f[h]) / p.cap));
-        const float m_new = fmaxf(fg + m, ig);
-        const float keep = expf(fg + m - m_new), put = expf(ig - m_new);
-        m = m_new;
-        float nq = 0.0f;
-        for (int i = threadIdx.x; i < D; i += blockDim.x) {          // a thread owns its entries of n
-            const float n = fmaf(put, row[p.off_k + h * D + i], keep * smem[i]);
-            smem[i] = n;
-            nq = fmaf(n, row[p.off_q + h * D + i] * qscale, nq);
+    float m_in = *mst;
+    const float bi = p.bias_i[h], bf = p.bias_f[h];
+    for (int t0 = first; t0 < end; t0 += 32) {
+        const int t = t0 + lane;
+        const bool valid = t < end;
+        float fg = 0.0f, ig = -INFINITY;                       // a token beyond the run leaves m as it is
+        if (valid) {
+            const float* row = p.proj + (size_t)t * p.ld;
+            ig = p.cap * tanhf((row[p.off_i + h] + bi) / p.cap);
+            fg = logsigmoidf_(p.cap * tanhf((row[p.off_f + h] + bf) / p.cap));
         }
-        nq = block_sum(nq, scratch);
-        if (threadIdx.x == 0) {
-            float* g = p.gates + ((size_t)t * H + h) * 3;
-            g[0] = keep; g[1] = put; g[2] = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
+        float a = fg, b = ig;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const float pa = __shfl_up_sync(0xffffffffu, a, off), pb = __shfl_up_sync(0xffffffffu, b, off);
+            if (lane >= off) { b = fmaxf(pb + a, b); a = pa + a; }
         }
+        const float m = fmaxf(a + m_in, b);
+        float m_prev = __shfl_up_sync(0xffffffffu, m, 1);
+        if (lane == 0) m_prev = m_in;
+        if (valid) {
+            float* g = p.gates + ((size_t)t * H + h) * 4;
+            g[0] = expf(fg + m_prev - m); g[1] = expf(ig - m); g[2] = expf(-m);
+        }
+        m_in = __shfl_sync(0xffffffffu, m, 31);
     }
-    if (first < end) {
-        for (int i = threadIdx.x; i < D; i += blockDim.x) nst[i] = smem[i];
-        if (threadIdx.x == 0) *mst = m;
-    }
+    if (lane == 0 && first < end) *mst = m_in;
 }
 
 __global__ void memory_scan_kernel(MemoryArgs p) {
@@ -201,11 +207,13 @@ __global__ void memory_scan_kernel(MemoryArgs p) {
     pdl_wait();
     const int s = blockIdx.x, h = blockIdx.y, VT = blockDim.x, j = blockIdx.z * VT + threadIdx.x;
     const int D = p.D, V = p.V, H = p.H;
-    const bool live = j < V;
+    const bool live = j <= V;                 // column V is n
     float* tile = smem;                       // [D][VT]
     float* vec = smem + (size_t)D * VT;       // 2 x (k[D], q[D])
-    float* S = p.state + (size_t)p.slots[s] * p.state_stride + (size_t)h * D * V;
-    load_tile(tile, S, D, V, j, live);
+    float* base = p.state + (size_t)p.slots[s] * p.state_stride;
+    float* S = base + (size_t)h * D * V;
+    float* nst = base + (size_t)H * D * V + (size_t)h * D;
+    load_tile(tile, S, D, V, j, live, nst);
     const int first = p.query_start[s], end = p.query_start[s + 1];
     const float qscale = 1.0f / sqrtf((float)D);
     for (int t = first; t < end; t++) {
@@ -216,21 +224,22 @@ __global__ void memory_scan_kernel(MemoryArgs p) {
             kb[i] = row[p.off_k + h * D + i];
             qb[i] = row[p.off_q + h * D + i] * qscale;
         }
-        const float* g = p.gates + ((size_t)t * H + h) * 3;
-        const float keep = g[0], put = g[1], den = g[2];
+        float* g = p.gates + ((size_t)t * H + h) * 4;
+        const float keep = g[0], put = g[1];
         __syncthreads();
         if (live) {
-            const float pv = put * row[p.off_v + h * V + j];
+            const float pv = put * (j < V ? row[p.off_v + h * V + j] : 1.0f);
             float o = 0.0f;
             for (int i = 0; i < D; i++) {
                 const float x = fmaf(kb[i], pv, keep * tile[i * VT + threadIdx.x]);
                 tile[i * VT + threadIdx.x] = x;
                 o = fmaf(x, qb[i], o);
             }
-            p.out[(size_t)t * H * V + h * V + j] = o / den;
+            if (j < V) p.out[(size_t)t * H * V + h * V + j] = o;
+            else g[3] = o;
         }
     }
-    store_tile(tile, S, D, V, j, live);
+    store_tile(tile, S, D, V, j, live, nst);
 }
 
 // ------------------------------------------------------------------- selective state space, scalar decay per head
@@ -282,6 +291,254 @@ __global__ void ssm_scan_kernel(SsmArgs p) {
     store_tile(tile, S, N, V, j, live);
 }
 
+// ------------------------------------------------------------------ the same recurrences, state in registers
+// For up to 256 state rows a block of 256 threads takes 32 value columns: lane = row group r (8 of them) + 8 x column
+// (4 per warp), and a thread keeps rows r RS .. r RS + RS - 1 of its column in registers.  A dot product over the rows
+// is RS multiply-adds and three shuffles; the per-token vectors live in shared memory, one padding word per row
+// group so that the eight groups read eight banks.  The state goes through a shared tile when it is loaded and
+// stored, so that global memory sees whole 128-byte rows.  A prompt portion of one request keeps 8 times the threads
+// of the kernels above busy; those stay for more than 256 rows.
+constexpr int RG = 8, RCOLS = 32, RTHREADS = 256;
+
+template <int RS>
+__device__ __forceinline__ void regs_load(float (&st)[RS], float* tile, const float* __restrict__ S, int D, int V, int col0,
+                                          const float* __restrict__ extra = nullptr) {
+    const int c = threadIdx.x & 31;
+    for (int i = threadIdx.x >> 5; i < RG * RS; i += RTHREADS / 32)
+        tile[i * 33 + c] = (i < D && col0 + c < V) ? S[(size_t)i * V + col0 + c]
+                                                   : ((extra && i < D && col0 + c == V) ? extra[i] : 0.0f);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, r = lane & 7, cc = (threadIdx.x >> 5) * 4 + (lane >> 3);
+#pragma unroll
+    for (int ii = 0; ii < RS; ii++) st[ii] = tile[(r * RS + ii) * 33 + cc];
+}
+template <int RS>
+__device__ __forceinline__ void regs_store(const float (&st)[RS], float* tile, float* __restrict__ S, int D, int V, int col0,
+                                           float* __restrict__ extra = nullptr) {
+    const int lane = threadIdx.x & 31, r = lane & 7, cc = (threadIdx.x >> 5) * 4 + (lane >> 3);
+    __syncthreads();
+#pragma unroll
+    for (int ii = 0; ii < RS; ii++) tile[(r * RS + ii) * 33 + cc] = st[ii];
+    __syncthreads();
+    const int c = threadIdx.x & 31;
+    for (int i = threadIdx.x >> 5; i < RG * RS; i += RTHREADS / 32)
+        if (i < D) {
+            if (col0 + c < V) S[(size_t)i * V + col0 + c] = tile[i * 33 + c];
+            else if (extra && col0 + c == V) extra[i] = tile[i * 33 + c];
+        }
+}
+__device__ __forceinline__ float rows_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+
+// One kernel for the three recurrences (MODE 0 delta rule, 1 matrix memory, 2 state space).  A run is walked in chunks
+// of CT tokens: while a chunk is computed from shared memory (no block-wide barrier between its tokens), the next
+// chunk's inputs are already on their way into registers; each warp then prepares its tokens of that chunk (unit
+// norms, decays, gates: a token's vector is spread over the warp's lanes, so its sums are warp sums) and stores
+// them into the other buffer.  Per token a thread does RS multiply-adds per dot product and one round of three
+// shuffles: the delta rule's two dot products S^T k and S^T q are both taken of the decayed state (o = q . S_decayed
+// + (k . q) u), so they share the round and the rank-one update is off the critical path.
+struct ScanArgs {
+    float* state; long long state_stride; float* out; const int* query_start; const int* slots;
+    int H, G, D, V;                        // D: rows of the state (key channels, or state size)
+    const float* x; int ld_x;              // delta, state space: [T, ...] after convolution and silu; matrix memory: the projection
+    const float* b; int ld_b;              // delta: write-strength logits [T, H]; state space: raw step sizes [T, H]
+    const float* a; int ld_a;              // delta: decay logits [T, H D]
+    const float* dt_bias; const float* A_log; const float* skip;
+    float key_eps;
+    int off_q, off_k, off_v;               // matrix memory: columns of x
+    float* gates;                          // matrix memory: [T, H, 4]
+};
+
+template <int MODE, int RS>
+__global__ void __launch_bounds__(RTHREADS) scan_chunks_kernel(ScanArgs p) {
+    extern __shared__ __align__(16) float smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int NV = MODE == 0 ? 3 : 2;
+    constexpr int VS = RG * (RS + 4);               // a vector in shared memory: row group r starts at r (RS + 4)
+    constexpr int TOK = NV * VS + 4 + RCOLS;        // vectors, four scalars, the block's 32 column values
+    constexpr int CT = RS == 32 ? 8 : 16, TPW = CT / 8, EPL = RS / 4;
+    const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * RCOLS;
+    const int D = p.D, V = p.V, H = p.H, grp = h / (H / p.G);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = lane & 7;
+    const int cw = warp * 4 + (lane >> 3), j = col0 + cw, base = r * (RS + 4);
+    const int n_cols = MODE == 1 ? V + 1 : V;       // (matrix memory: column V is n)
+    const bool live = j < n_cols;
+    float* tile = smem;                             // [RG RS][33], used when the state is loaded and stored
+    float* chunks = smem + RG * RS * 33;            // 2 x CT x TOK
+    float* sbase = p.state + (size_t)p.slots[s] * p.state_stride;
+    float* S = sbase + (size_t)h * D * V;
+    float* extra = MODE == 1 ? sbase + (size_t)H * D * V + (size_t)h * D : nullptr;
+    float st[RS];
+    for (int i = threadIdx.x; i < 2 * CT * TOK; i += RTHREADS) chunks[i] = 0.0f;
+    regs_load<RS>(st, tile, S, D, V, col0, extra);
+    const int first = p.query_start[s], end = p.query_start[s + 1];
+    const float rate = MODE == 1 ? 0.0f : expf(p.A_log[h]);
+    const float qscale = 1.0f / sqrtf((float)D);
+    // where this head's vectors start in a row of x
+    const int off0 = MODE == 0 ? p.G * D + grp * D : (MODE == 1 ? p.off_k + h * D : H * V + grp * D);               // k | k | B
+    const int off1 = MODE == 0 ? grp * D : (MODE == 1 ? p.off_q + h * D : H * V + p.G * D + grp * D);               // q | q | C
+    const int off_col = MODE == 0 ? 2 * p.G * D + h * V : (MODE == 1 ? p.off_v + h * V : h * V);                    // v | v | x
+
+    float f0[TPW][EPL], f1[TPW][EPL], f2[TPW][EPL], fc[TPW], fs[TPW];
+    auto prefetch = [&](int t0) {
+#pragma unroll
+        for (int w = 0; w < TPW; w++) {
+            const int t = t0 + warp + 8 * w;
+            if (t >= end) continue;
+            const float* row = p.x + (size_t)t * p.ld_x;
+#pragma unroll
+            for (int m = 0; m < EPL; m++) {
+                const int i = lane + 32 * m;
+                if (i < D) {
+                    f0[w][m] = row[off0 + i];
+                    f1[w][m] = row[off1 + i];
+                    if (MODE == 0) f2[w][m] = p.a[(size_t)t * p.ld_a + h * D + i];
+                }
+            }
+            const int c = col0 + lane;
+            fc[w] = c < V ? row[off_col + c] : 1.0f;
+            if (MODE != 1) fs[w] = p.b[(size_t)t * p.ld_b + h];
+        }
+    };
+    auto prepare = [&](int t0, float* buf) {
+#pragma unroll
+        for (int w = 0; w < TPW; w++) {
+            const int tt = warp + 8 * w, t = t0 + tt;
+            if (t >= end) continue;
+            float* tok = buf + tt * TOK;
+            float s0 = 0.0f, s1 = 0.0f, s01 = 0.0f;
+#pragma unroll
+            for (int m = 0; m < EPL; m++) {
+                const int i = lane + 32 * m;
+                if (i < D) {
+                    const int vi = i + (i / RS) * 4;
+                    tok[vi] = f0[w][m];
+                    tok[VS + vi] = MODE == 1 ? f1[w][m] * qscale : f1[w][m];
+                    if (MODE == 0) {
+                        tok[2 * VS + vi] = expf(-rate * softplusf_(f2[w][m] + p.dt_bias[h * D + i]));
+                        s0 = fmaf(f0[w][m], f0[w][m], s0); s1 = fmaf(f1[w][m], f1[w][m], s1); s01 = fmaf(f0[w][m], f1[w][m], s01);
+                    }
+                }
+            }
+            tok[NV * VS + 4 + lane] = fc[w];
+            if (MODE == 0) {
+                s0 = warp_sum(s0); s1 = warp_sum(s1); s01 = warp_sum(s01);
+                if (lane == 0) {
+                    tok[NV * VS + 0] = 1.0f / sqrtf(s0 + p.key_eps);            // 1 / |k|
+                    tok[NV * VS + 1] = qscale / sqrtf(s1 + p.key_eps);          // D^-1/2 / |q|
+                    tok[NV * VS + 2] = s01;                                     // k . q, before the norms
+                    tok[NV * VS + 3] = sigmoidf_(fs[w]);
+                }
+            } else if (MODE == 1) {
+                if (lane == 0) {
+                    const float* g = p.gates + ((size_t)t * H + h) * 4;
+                    tok[NV * VS + 0] = g[0]; tok[NV * VS + 1] = g[1];
+                }
+            } else if (lane == 0) {
+                const float dt = softplusf_(fs[w] + p.dt_bias[h]);
+                tok[NV * VS + 0] = expf(-rate * dt); tok[NV * VS + 1] = dt;
+            }
+        }
+    };
+
+    const float skip = MODE == 2 ? p.skip[h] : 0.0f;
+    prefetch(first);
+    prepare(first, chunks);
+    __syncthreads();
+    int cur = 0;
+    for (int t0 = first; t0 < end; t0 += CT, cur ^= 1) {
+        const bool more = t0 + CT < end;
+        if (more) prefetch(t0 + CT);
+        const int n = min(CT, end - t0);
+        const float* buf = chunks + cur * CT * TOK;
+        for (int tt = 0; tt < n; tt++) {
+            const float* tok = buf + tt * TOK;
+            const float4 sc = *reinterpret_cast<const float4*>(tok + NV * VS);
+            const float val = tok[NV * VS + 4 + cw];
+            const float4* v0 = reinterpret_cast<const float4*>(tok + base);
+            const float4* v1 = reinterpret_cast<const float4*>(tok + VS + base);
+            float o;
+            if (MODE == 0) {
+                const float4* v2 = reinterpret_cast<const float4*>(tok + 2 * VS + base);
+                float ak = 0.0f, aq = 0.0f;
+#pragma unroll
+                for (int i4 = 0; i4 < RS / 4; i4++) {
+                    const float4 k = v0[i4], q = v1[i4], g = v2[i4];
+                    st[4 * i4 + 0] *= g.x; st[4 * i4 + 1] *= g.y; st[4 * i4 + 2] *= g.z; st[4 * i4 + 3] *= g.w;
+                    ak = fmaf(st[4 * i4 + 3], k.w, fmaf(st[4 * i4 + 2], k.z, fmaf(st[4 * i4 + 1], k.y, fmaf(st[4 * i4], k.x, ak))));
+                    aq = fmaf(st[4 * i4 + 3], q.w, fmaf(st[4 * i4 + 2], q.z, fmaf(st[4 * i4 + 1], q.y, fmaf(st[4 * i4], q.x, aq))));
+                }
+#pragma unroll
+                for (int off = 1; off < 8; off <<= 1) {
+                    ak += __shfl_xor_sync(0xffffffffu, ak, off);
+                    aq += __shfl_xor_sync(0xffffffffu, aq, off);
+                }
+                const float uk = sc.w * (val - ak * sc.x) * sc.x;              // beta (v - S^T k) / |k|
+                o = sc.y * fmaf(uk, sc.z, aq);
+#pragma unroll
+                for (int i4 = 0; i4 < RS / 4; i4++) {
+                    const float4 k = v0[i4];
+                    st[4 * i4 + 0] = fmaf(k.x, uk, st[4 * i4 + 0]); st[4 * i4 + 1] = fmaf(k.y, uk, st[4 * i4 + 1]);
+                    st[4 * i4 + 2] = fmaf(k.z, uk, st[4 * i4 + 2]); st[4 * i4 + 3] = fmaf(k.w, uk, st[4 * i4 + 3]);
+                }
+            } else {
+                const float keep = sc.x, pv = sc.y * val;                       // put v | dt x
+                float acc = 0.0f;
+#pragma unroll
+                for (int i4 = 0; i4 < RS / 4; i4++) {
+                    const float4 k = v0[i4], q = v1[i4];
+                    st[4 * i4 + 0] = fmaf(k.x, pv, keep * st[4 * i4 + 0]); st[4 * i4 + 1] = fmaf(k.y, pv, keep * st[4 * i4 + 1]);
+                    st[4 * i4 + 2] = fmaf(k.z, pv, keep * st[4 * i4 + 2]); st[4 * i4 + 3] = fmaf(k.w, pv, keep * st[4 * i4 + 3]);
+                    acc = fmaf(st[4 * i4 + 3], q.w, fmaf(st[4 * i4 + 2], q.z, fmaf(st[4 * i4 + 1], q.y, fmaf(st[4 * i4], q.x, acc))));
+                }
+                o = rows_sum(acc);
+                if (MODE == 2) o = fmaf(skip, val, o);
+            }
+            if (live && r == 0) {
+                const int t = t0 + tt;
+                if (j < V) p.out[(size_t)t * H * V + h * V + j] = o;
+                else p.gates[((size_t)t * H + h) * 4 + 3] = o;
+            }
+        }
+        if (more) prepare(t0 + CT, chunks + (cur ^ 1) * CT * TOK);
+        __syncthreads();
+    }
+    regs_store<RS>(st, tile, S, D, V, col0, extra);
+}
+
+inline int rows_per_thread(int D) { return D <= 32 ? 4 : (D <= 64 ? 8 : (D <= 128 ? 16 : (D <= 256 ? 32 : 0))); }
+inline bool regs_kernels_on() {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("EMBER_SCAN_IN_REGISTERS"); on = (e && e[0] == '0') ? 0 : 1; }
+    return on != 0;
+}
+
+template <int MODE, int RS>
+inline int launch_scan_rs(const ScanArgs& p, int S, int n_cols, cudaStream_t st) {
+    constexpr int NV = MODE == 0 ? 3 : 2, CT = RS == 32 ? 8 : 16;
+    const size_t smem = ((size_t)RG * RS * 33 + 2 * CT * (NV * RG * (RS + 4) + 4 + RCOLS)) * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(scan_chunks_kernel<MODE, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail("scan: %s", cudaGetErrorString(e));
+    }
+    launch_kernel(scan_chunks_kernel<MODE, RS>, dim3(S, p.H, (n_cols + RCOLS - 1) / RCOLS), RTHREADS, smem, st, p);
+    return 0;
+}
+template <int MODE>
+inline int launch_scan(const ScanArgs& p, int S, int n_cols, cudaStream_t st) {
+    switch (rows_per_thread(p.D)) {
+        case 4: return launch_scan_rs<MODE, 4>(p, S, n_cols, st);
+        case 8: return launch_scan_rs<MODE, 8>(p, S, n_cols, st);
+        case 16: return launch_scan_rs<MODE, 16>(p, S, n_cols, st);
+        default: return launch_scan_rs<MODE, 32>(p, S, n_cols, st);
+    }
+}
+
 // Columns per block: whole warps, at most 128, fewer while the state tile would not fit in shared memory.
 inline int pick_columns(int D, int V, int extra_floats, size_t* smem) {
     int warps = (V + 31) / 32;
@@ -331,6 +588,14 @@ EMBER_API int ember_delta_scan(const float* conv, int ld_conv, const float* beta
     const int VT = pick_columns(D, V, 6 * D + 128, &smem);
     if (allow_smem(delta_scan_kernel, smem, "delta_scan")) return 1;
     DeltaArgs p{conv, ld_conv, beta, ld_beta, a, ld_a, dt_bias, A_log, state, state_stride, out, query_start, slots, H, G, D, V, key_eps};
+    if (rows_per_thread(D) && regs_kernels_on()) {
+        ScanArgs q{};
+        q.state = state; q.state_stride = state_stride; q.out = out; q.query_start = query_start; q.slots = slots;
+        q.H = H; q.G = G; q.D = D; q.V = V; q.x = conv; q.ld_x = ld_conv; q.b = beta; q.ld_b = ld_beta; q.a = a; q.ld_a = ld_a;
+        q.dt_bias = dt_bias; q.A_log = A_log; q.key_eps = key_eps;
+        if (launch_scan<0>(q, S, V, (cudaStream_t)stream)) return 1;
+        return check_launch("delta_scan");
+    }
     launch_kernel(delta_scan_kernel, dim3(S, H, (V + VT - 1) / VT), VT, smem, (cudaStream_t)stream, p);
     return check_launch("delta_scan");
 }
@@ -342,14 +607,20 @@ EMBER_API int ember_memory_scan(const float* proj, int ld, int off_q, int off_k,
     if (S <= 0) return 0;
     if (H <= 0 || D <= 0 || V <= 0 || !(cap > 0.0f)) return fail("memory_scan: %d heads of %d x %d, cap %g", H, D, V, cap);
     if (S > 65535 || H > 65535) return fail("memory_scan: too many runs or heads for one launch");
-    size_t smem;
-    const int VT = pick_columns(D, V, 4 * D, &smem);
-    if (allow_smem(memory_scan_kernel, smem, "memory_scan")) return 1;
-    if (allow_smem(memory_gates_kernel, (size_t)D * sizeof(float), "memory_scan")) return 1;
+    cudaStream_t st = (cudaStream_t)stream;
     MemoryArgs p{proj, ld, off_q, off_k, off_v, off_i, off_f, bias_i, bias_f, cap, state, state_stride, gates, out, query_start, slots, H, D, V};
-    const int gate_threads = D >= 256 ? 256 : (D + 31) / 32 * 32;
-    launch_kernel(memory_gates_kernel, dim3(S, H), gate_threads, (size_t)D * sizeof(float), (cudaStream_t)stream, p);
-    launch_kernel(memory_scan_kernel, dim3(S, H, (V + VT - 1) / VT), VT, smem, (cudaStream_t)stream, p);
+    launch_kernel(memory_gates_kernel, dim3(S, H), 32, 0, st, p);
+    if (rows_per_thread(D) && regs_kernels_on()) {
+        ScanArgs q{};
+        q.state = state; q.state_stride = state_stride; q.out = out; q.query_start = query_start; q.slots = slots;
+        q.H = H; q.G = H; q.D = D; q.V = V; q.x = proj; q.ld_x = ld; q.off_q = off_q; q.off_k = off_k; q.off_v = off_v; q.gates = gates;
+        if (launch_scan<1>(q, S, V + 1, st)) return 1;
+        return check_launch("memory_scan");
+    }
+    size_t smem;
+    const int VT = pick_columns(D, V + 1, 4 * D, &smem);
+    if (allow_smem(memory_scan_kernel, smem, "memory_scan")) return 1;
+    launch_kernel(memory_scan_kernel, dim3(S, H, (V + 1 + VT - 1) / VT), VT, smem, st, p);
     return check_launch("memory_scan");
 }
 
@@ -363,6 +634,14 @@ EMBER_API int ember_ssm_scan(const float* conv, int ld_conv, const float* dt, in
     const int VT = pick_columns(N, V, 4 * N, &smem);
     if (allow_smem(ssm_scan_kernel, smem, "ssm_scan")) return 1;
     SsmArgs p{conv, ld_conv, dt, ld_dt, dt_bias, A_log, skip, state, state_stride, out, query_start, slots, H, G, N, V};
+    if (rows_per_thread(N) && regs_kernels_on()) {
+        ScanArgs q{};
+        q.state = state; q.state_stride = state_stride; q.out = out; q.query_start = query_start; q.slots = slots;
+        q.H = H; q.G = G; q.D = N; q.V = V; q.x = conv; q.ld_x = ld_conv; q.b = dt; q.ld_b = ld_dt; q.dt_bias = dt_bias;
+        q.A_log = A_log; q.skip = skip;
+        if (launch_scan<2>(q, S, V, (cudaStream_t)stream)) return 1;
+        return check_launch("ssm_scan");
+    }
     launch_kernel(ssm_scan_kernel, dim3(S, H, (V + VT - 1) / VT), VT, smem, (cudaStream_t)stream, p);
     return check_launch("ssm_scan");
 }

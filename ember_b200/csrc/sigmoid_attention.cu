@@ -5,8 +5,9 @@
 // rotate_store: rotate-half rotation of the first `rotary` elements of every query and key head (pair (i, i +
 // rotary / 2), angle = float(position) * inv_freq[i] in fp32), queries to q_out, keys and values into the request's
 // pages: k_pool [pages, kv_heads, page, D], v_pool [pages, kv_heads, page, V].
-// attend: one block per (tile of up to 16 consecutive queries of a run, query head); keys are walked in tiles of 32
-// in ascending order, so an output's sum has the same order however the tokens were cut into steps.
+// attend: one block per (tile of consecutive queries of a run, heads of one key/value head): 16 (token, head) rows;
+// keys are walked in tiles of 32 in ascending order, so an output's sum has the same order however the tokens were
+// cut into steps.
 #include "common.cuh"
 
 EMBER_DEFINE_LAST_ERROR
@@ -58,29 +59,55 @@ __global__ void rotate_store_kernel(const float* __restrict__ qkv, int ld, int H
 
 constexpr int SA_ROWS = 16, SA_KEYS = 32, SA_THREADS = 128;
 
-// CM: value columns per thread (V <= 128 CM)
+// 8 consecutive elements of a cache row as floats (16-byte loads where the row allows them)
+__device__ __forceinline__ void load_row_chunk(const __nv_bfloat16* src, float* dst, int n, bool whole) {
+    if (whole) {
+        const uint4 u = *reinterpret_cast<const uint4*>(src);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; i++) { const float2 f = __bfloat1622float2(h[i]); dst[2 * i] = f.x; dst[2 * i + 1] = f.y; }
+    } else {
+        for (int i = 0; i < n; i++) dst[i] = __bfloat162float(src[i]);
+    }
+}
+__device__ __forceinline__ void load_row_chunk(const float* src, float* dst, int n, bool whole) {
+    if (whole) {
+        const float4 a = reinterpret_cast<const float4*>(src)[0], b = reinterpret_cast<const float4*>(src)[1];
+        dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w; dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+    } else {
+        for (int i = 0; i < n; i++) dst[i] = src[i];
+    }
+}
+
+// A block's rows are (query token, query head) pairs of one key/value head: `hpb` heads (a divisor of the group, at
+// most 16) of 16 / hpb consecutive tokens, so a decode step reads a request's keys once for all heads of the group
+// and a prompt portion fills the 16 rows.  Scores: a thread takes one key and four rows, four elements at a time;
+// read-out: a thread takes value columns tid, tid + 128, ... of all rows, four keys at a time.
+// CM: value columns per thread (V <= 128 CM).  Head sizes that are multiples of 8 are fetched with 16-byte loads.
 template <typename T, int CM>
 __global__ void __launch_bounds__(SA_THREADS)
 sigmoid_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
-                         T* __restrict__ out, int H, int G, int D, int V, const int* __restrict__ tiles,
+                         T* __restrict__ out, int H, int G, int D, int V, int hpb, const int* __restrict__ tiles,
                          const int* __restrict__ block_table, int max_blocks, int page, int num_pages, float scale,
                          const float* __restrict__ head_bias, int* __restrict__ err) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
     pdl_wait();
     const int* tile = tiles + 4 * blockIdx.x;
     const int run = tile[0], row0 = tile[1], nq = tile[2], pos0 = tile[3];
-    const int h = blockIdx.y, kv = h / (H / G);
-    const int DP = D + 1;
-    float* qs = smem;                                   // [SA_ROWS][D]
-    float* ks = qs + SA_ROWS * D;                       // [SA_KEYS][D + 1]
-    float* vs = ks + SA_KEYS * DP;                      // [SA_KEYS][V]
-    float* ws = vs + SA_KEYS * V;                       // [SA_ROWS][SA_KEYS]
-    for (int e = threadIdx.x; e < SA_ROWS * D; e += SA_THREADS) {
-        const int r = e / D, i = e - r * D;
-        qs[e] = r < nq ? to_float(q[((size_t)(row0 + r) * H + h) * D + i]) : 0.0f;
+    const int h0 = blockIdx.y * hpb, kv = h0 / (H / G);
+    const int n_rows = nq * hpb;                        // row rr: token rr / hpb, head h0 + rr % hpb
+    const int DP = (D + 3) / 4 * 4 + 4, VP = (V + 3) / 4 * 4;
+    float* qs = smem;                                   // [SA_ROWS][DP]
+    float* ks = qs + SA_ROWS * DP;                      // [SA_KEYS][DP]
+    float* vs = ks + SA_KEYS * DP;                      // [SA_KEYS][VP]
+    float* ws = vs + SA_KEYS * VP;                      // [SA_ROWS][SA_KEYS]
+    for (int e = threadIdx.x; e < SA_ROWS * DP; e += SA_THREADS) {
+        const int r = e / DP, i = e - r * DP;
+        qs[e] = (r < n_rows && i < D) ? to_float(q[((size_t)(row0 + r / hpb) * H + h0 + r % hpb) * D + i]) : 0.0f;
     }
-    const float bias = head_bias ? head_bias[h] : 0.0f;
+    for (int e = threadIdx.x; e < SA_KEYS * (DP - D); e += SA_THREADS)       // the padding of key rows stays zero
+        ks[(e / (DP - D)) * DP + D + e % (DP - D)] = 0.0f;
     float acc[SA_ROWS][CM];
 #pragma unroll
     for (int r = 0; r < SA_ROWS; r++)
@@ -89,79 +116,106 @@ sigmoid_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
     const int n_keys = pos0 + nq;                       // keys 0 .. position of the last query
     const int* bt = block_table + (size_t)run * max_blocks;
     const int kk = threadIdx.x & 31, rg = threadIdx.x >> 5;
+    const int dchunks = (D + 7) / 8, vchunks = (V + 7) / 8;
+    const bool d8 = (D & 7) == 0, v8 = (V & 7) == 0;
     for (int k0 = 0; k0 < n_keys; k0 += SA_KEYS) {
         __syncthreads();
-        // keys and values of this tile (rows beyond the last key are zero)
-        for (int e = threadIdx.x; e < SA_KEYS * D; e += SA_THREADS) {
-            const int r = e / D, i = e - r * D, kp = k0 + r;
-            float v = 0.0f;
-            if (kp < n_keys) {
-                const int blk = bt[kp / page];
-                if (blk >= 0 && blk < num_pages) v = to_float(k_pool[(((size_t)blk * G + kv) * page + kp % page) * D + i]);
-                else if (err) atomicOr(err, EMBER_ERR_PAGE_RANGE);
+        // keys and values of this tile as floats (rows beyond the last key are zero)
+        for (int e = threadIdx.x; e < SA_KEYS * dchunks; e += SA_THREADS) {
+            const int r = e / dchunks, c = e - r * dchunks, kp = k0 + r, n = min(8, D - 8 * c);
+            float* dst = ks + r * DP + 8 * c;
+            const int blk = kp < n_keys ? bt[kp / page] : -1;
+            if (blk >= 0 && blk < num_pages) {
+                load_row_chunk(k_pool + (((size_t)blk * G + kv) * page + kp % page) * D + 8 * c, dst, n, d8);
+            } else {
+                if (kp < n_keys && err) atomicOr(err, EMBER_ERR_PAGE_RANGE);
+                for (int i = 0; i < n; i++) dst[i] = 0.0f;
             }
-            ks[r * DP + i] = v;
         }
-        for (int e = threadIdx.x; e < SA_KEYS * V; e += SA_THREADS) {
-            const int r = e / V, i = e - r * V, kp = k0 + r;
-            float v = 0.0f;
-            if (kp < n_keys) {
-                const int blk = bt[kp / page];
-                if (blk >= 0 && blk < num_pages) v = to_float(v_pool[(((size_t)blk * G + kv) * page + kp % page) * V + i]);
+        for (int e = threadIdx.x; e < SA_KEYS * vchunks; e += SA_THREADS) {
+            const int r = e / vchunks, c = e - r * vchunks, kp = k0 + r, n = min(8, V - 8 * c);
+            float* dst = vs + r * VP + 8 * c;
+            const int blk = kp < n_keys ? bt[kp / page] : -1;
+            if (blk >= 0 && blk < num_pages) {
+                load_row_chunk(v_pool + (((size_t)blk * G + kv) * page + kp % page) * V + 8 * c, dst, n, v8);
+            } else {
+                for (int i = 0; i < n; i++) dst[i] = 0.0f;
             }
-            vs[e] = v;
-        }
-        __syncthreads();
-        // weights: thread (key kk, rows rg, rg + 4, ...)
-#pragma unroll
-        for (int m = 0; m < SA_ROWS / 4; m++) {
-            const int r = rg + 4 * m;
-            float sc = 0.0f;
-            for (int i = 0; i < D; i++) sc = fmaf(qs[r * D + i], ks[kk * DP + i], sc);
-            const bool seen = r < nq && k0 + kk <= pos0 + r;
-            ws[r * SA_KEYS + kk] = seen ? 1.0f / (1.0f + expf(-(sc * scale + bias))) : 0.0f;
         }
         __syncthreads();
-        const int last = min(SA_KEYS, n_keys - k0);
-        for (int x = 0; x < last; x++) {
-            float vv[CM];
+        // weights: thread (key kk, rows rg, rg + 4, rg + 8, rg + 12)
+        if (rg < n_rows) {
+            float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const float4* kp4 = reinterpret_cast<const float4*>(ks + kk * DP);
+            for (int i = 0; i < DP / 4 - 1; i++) {
+                const float4 kx = kp4[i];
 #pragma unroll
-            for (int m = 0; m < CM; m++) {
-                const int c = threadIdx.x + m * SA_THREADS;
-                vv[m] = c < V ? vs[x * V + c] : 0.0f;
+                for (int m = 0; m < 4; m++) {
+                    const float4 qx = reinterpret_cast<const float4*>(qs + (rg + 4 * m) * DP)[i];
+                    sc[m] = fmaf(qx.x, kx.x, fmaf(qx.y, kx.y, fmaf(qx.z, kx.z, fmaf(qx.w, kx.w, sc[m]))));
+                }
             }
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                const int r = rg + 4 * m;
+                const bool seen = r < n_rows && k0 + kk <= pos0 + r / hpb;
+                const float b = head_bias ? head_bias[h0 + r % hpb] : 0.0f;
+                ws[r * SA_KEYS + kk] = seen ? 1.0f / (1.0f + expf(-(sc[m] * scale + b))) : 0.0f;
+            }
+        }
+        __syncthreads();
+        for (int x = 0; x < SA_KEYS; x += 4) {
+            if (k0 + x >= n_keys) break;
+            float vv[4][CM];
+#pragma unroll
+            for (int y = 0; y < 4; y++)
+#pragma unroll
+                for (int m = 0; m < CM; m++) {
+                    const int c = threadIdx.x + m * SA_THREADS;
+                    vv[y][m] = c < V ? vs[(x + y) * VP + c] : 0.0f;
+                }
 #pragma unroll
             for (int r = 0; r < SA_ROWS; r++) {
-                const float w = ws[r * SA_KEYS + x];
+                if (r >= n_rows) break;
+                const float4 w = *reinterpret_cast<const float4*>(ws + r * SA_KEYS + x);
 #pragma unroll
-                for (int m = 0; m < CM; m++) acc[r][m] = fmaf(w, vv[m], acc[r][m]);
+                for (int m = 0; m < CM; m++)
+                    acc[r][m] = fmaf(w.w, vv[3][m], fmaf(w.z, vv[2][m], fmaf(w.y, vv[1][m], fmaf(w.x, vv[0][m], acc[r][m]))));
             }
         }
     }
 #pragma unroll
     for (int r = 0; r < SA_ROWS; r++) {
-        if (r >= nq) break;
+        if (r >= n_rows) break;
 #pragma unroll
         for (int m = 0; m < CM; m++) {
             const int c = threadIdx.x + m * SA_THREADS;
-            if (c < V) out[((size_t)(row0 + r) * H + h) * V + c] = from_float<T>(acc[r][m]);
+            if (c < V) out[((size_t)(row0 + r / hpb) * H + h0 + r % hpb) * V + c] = from_float<T>(acc[r][m]);
         }
     }
+}
+
+// Query heads per block: the largest divisor of the group that is at most 16.
+inline int heads_per_block(int group) {
+    int h = group < SA_ROWS ? group : SA_ROWS;
+    while (group % h) h--;
+    return h;
 }
 
 template <typename T>
 int launch_attend(const void* q, const void* k_pool, const void* v_pool, void* out, int H, int G, int D, int V,
                   const int* tiles, int n_tiles, const int* bt, int max_blocks, int page, int num_pages, float scale,
                   const float* head_bias, int* err, cudaStream_t st) {
-    const size_t smem = ((size_t)SA_ROWS * D + (size_t)SA_KEYS * (D + 1) + (size_t)SA_KEYS * V + SA_ROWS * SA_KEYS) * sizeof(float);
+    const int DP = (D + 3) / 4 * 4 + 4, VP = (V + 3) / 4 * 4, hpb = heads_per_block(H / G);
+    const size_t smem = ((size_t)(SA_ROWS + SA_KEYS) * DP + (size_t)SA_KEYS * VP + SA_ROWS * SA_KEYS) * sizeof(float);
     if (smem > 200 * 1024) return fail("sigmoid_attention: heads of %d / %d do not fit in shared memory", D, V);
     const int cm = (V + SA_THREADS - 1) / SA_THREADS;
 #define EMBER_SA_LAUNCH(CM)                                                                                              \
     do {                                                                                                                 \
         if (smem > 48 * 1024)                                                                                            \
             cudaFuncSetAttribute(sigmoid_attention_kernel<T, CM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        launch_kernel(sigmoid_attention_kernel<T, CM>, dim3(n_tiles, H), SA_THREADS, smem, st, (const T*)q, (const T*)k_pool,  \
-                      (const T*)v_pool, (T*)out, H, G, D, V, tiles, bt, max_blocks, page, num_pages, scale, head_bias, err); \
+        launch_kernel(sigmoid_attention_kernel<T, CM>, dim3(n_tiles, H / hpb), SA_THREADS, smem, st, (const T*)q, (const T*)k_pool, \
+                      (const T*)v_pool, (T*)out, H, G, D, V, hpb, tiles, bt, max_blocks, page, num_pages, scale, head_bias, err); \
     } while (0)
     if (cm <= 1) EMBER_SA_LAUNCH(1);
     else if (cm == 2) EMBER_SA_LAUNCH(2);
@@ -175,7 +229,7 @@ int launch_attend(const void* q, const void* k_pool, const void* v_pool, void* o
 
 using namespace ember;
 
-EMBER_API int ember_sigmoid_attention_tile_queries() { return SA_ROWS; }
+EMBER_API int ember_sigmoid_attention_tile_queries(int group) { return group > 0 ? SA_ROWS / heads_per_block(group) : 0; }
 
 EMBER_API int ember_rotate_store(const float* qkv, int ld, int T, int H, int G, int D, int V, const float* inv_freq, int rotary,
                                  const int* positions, const int* seq_of, const int* block_table, int max_blocks, int page,

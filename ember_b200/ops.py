@@ -605,10 +605,11 @@ GATE_NONE, GATE_SIGMOID_AFTER, GATE_SILU_BEFORE = 0, 1, 2
 
 def group_norm_gate(x: torch.Tensor, x_col: int, gate: Optional[torch.Tensor], gate_col: int, weight: torch.Tensor,
                     per_group_weight: bool, eps: float, gate_mode: int, out: torch.Tensor, T: int, groups: int, width: int,
-                    stream: Optional[int] = None) -> None:
+                    den: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
     """A token's ``groups * width`` values (fp32, from column ``x_col`` of x's rows), each group divided by its root
     mean square and multiplied by ``weight`` (one for all groups or one per group); the gate (fp32 rows, from column
-    ``gate_col``) is a sigmoid after the norm or a silu before it."""
+    ``gate_col``) is a sigmoid after the norm or a silu before it.  ``den`` (fp32 [T, groups, 4], what ``memory_scan``
+    leaves): every group is first divided by max(|den[.., 3]|, den[.., 2]) + 1e-6."""
     _check(x, "x", torch.float32)
     _check(weight, "weight", torch.float32)
     _check(out, "out")
@@ -620,10 +621,14 @@ def group_norm_gate(x: torch.Tensor, x_col: int, gate: Optional[torch.Tensor], g
         _check(gate, "gate", torch.float32)
         if gate.dim() != 2 or gate.shape[0] < T or gate_col + groups * width > gate.shape[1]:
             raise KernelError("group_norm_gate: the gate does not fit")
+    if den is not None:
+        _check(den, "den", torch.float32)
+        if den.numel() < T * groups * 4:
+            raise KernelError("group_norm_gate: the denominators do not fit")
     lib = _lib("norm_gate")
     _call(lib, lib.ember_group_norm_gate, _off(x, x_col), c_int(x.shape[1]), _off(gate, gate_col) if gate_mode else c_void_p(0),
           c_int(gate.shape[1] if gate_mode else 0), _p(weight), c_int(width if per_group_weight else 0), c_float(eps),
-          c_int(gate_mode), _p(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(groups), c_int(width), _stream(stream))
+          c_int(gate_mode), _p(den), _p(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(groups), c_int(width), _stream(stream))
 
 
 def scaled_sum(x: torch.Tensor, a: float, y: Optional[torch.Tensor], b: float, out: torch.Tensor, n: int,
@@ -706,12 +711,13 @@ def memory_scan(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, off_i: i
                 stream: Optional[int] = None) -> None:
     """Matrix memory with exponential input gate and running maximum over the step's runs.  ``proj`` fp32 [T, ld]
     holds q, k, v and the two gates' logits at the given columns; the state row of a request is S [heads, dim, vdim],
-    n [heads, dim], m [heads]; ``gates`` fp32 scratch [T, heads, 3]; out fp32 [T, heads vdim]."""
+    n [heads, dim], m [heads].  Leaves out fp32 [T, heads vdim] = S^T q and ``gates`` fp32 [T, heads, 4] = (keep, put,
+    e^-m, n . q): the read-out is out / (max(|n . q|, e^-m) + 1e-6), which ``group_norm_gate`` applies (``den``)."""
     for t, n in ((proj, "proj"), (bias_i, "bias_i"), (bias_f, "bias_f"), (state, "state"), (gates, "gates"), (out, "out")):
         _check(t, n, torch.float32)
     _check_runs(query_start, slots, S)
     if state.dim() != 2 or state.shape[1] < heads * dim * vdim + heads * dim + heads or bias_i.numel() != heads or \
-            bias_f.numel() != heads:
+            bias_f.numel() != heads or gates.numel() < proj.shape[0] * heads * 4:
         raise KernelError("memory_scan: buffers do not fit the head geometry")
     lib = _lib("recurrent")
     _call(lib, lib.ember_memory_scan, _p(proj), c_int(proj.shape[1]), c_int(off_q), c_int(off_k), c_int(off_v), c_int(off_i),
@@ -737,7 +743,13 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, dt_col: int, dt_bias: torch.T
 
 
 # ------------------------------------------------------- attention without softmax (csrc/sigmoid_attention.cu)
-SIGMOID_ATTENTION_TILE_QUERIES = 16
+def sigmoid_attention_tile_queries(group: int) -> int:
+    """Query tokens per tile: a block's 16 rows are (token, head) pairs over the largest divisor of the group that
+    is at most 16 (the rule of ember_sigmoid_attention_tile_queries)."""
+    h = min(group, 16)
+    while group % h:
+        h -= 1
+    return 16 // h
 
 
 def rotate_store(qkv: torch.Tensor, T: int, heads: int, kv_heads: int, dim: int, vdim: int, inv_freq: Optional[torch.Tensor],

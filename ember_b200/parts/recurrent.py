@@ -177,13 +177,13 @@ class MatrixMemory(_StateMixer):
         off_k, off_v, off_g = self.qk, 2 * self.qk, 2 * self.qk + self.vd
         off_i = off_g + self.vd
         proj = ctx.buf("mlstm.proj", (mt, off_i + 2 * H), torch.float32)
-        gates = ctx.buf("mlstm.gates", (mt, H, 3), torch.float32)
+        gates = ctx.buf("mlstm.gates", (mt, H, 4), torch.float32)
         o = ctx.buf("mlstm.read", (mt, self.vd), torch.float32)
         y = ctx.buf("mlstm.normed", (mt, self.vd), rt.dtype)
         self.in_proj(ctx, x, proj, T, ops.EPI_STORE_F32)
         ops.memory_scan(proj, 0, off_k, off_v, off_i, off_i + H, self.bias_i, self.bias_f, s.gate_cap, cache.state, gates, o,
                         ctx.query_start, ctx.state_slots, ctx.S, H, D, V, stream=ctx.stream)
-        ops.group_norm_gate(o, 0, proj, off_g, self.norm_w, True, s.norm_eps, ops.GATE_SIGMOID_AFTER, y, T, H, V,
+        ops.group_norm_gate(o, 0, proj, off_g, self.norm_w, True, s.norm_eps, ops.GATE_SIGMOID_AFTER, y, T, H, V, den=gates,
                             stream=ctx.stream)
         self._out(ctx, y, out, accumulate)
 

@@ -56,7 +56,7 @@ class SigmoidAttention(Mixer):
         return CacheNeed(kind="full", num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, value_dim=s.value_dim)
 
     def tile_requests(self):
-        return [(ops.SIGMOID_ATTENTION_TILE_QUERIES, "all")]
+        return [(ops.sigmoid_attention_tile_queries(self.spec.num_heads // self.spec.num_kv_heads), "all")]
 
     def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
         s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
@@ -68,7 +68,7 @@ class SigmoidAttention(Mixer):
         self.qkv(ctx, x, qkv, T, ops.EPI_STORE_F32)
         ops.rotate_store(qkv, T, H, G, D, V, self.inv_freq, self.rotary, ctx.positions, ctx.seq_of, table, cache.page_tokens,
                          cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err, stream=ctx.stream)
-        tiles, n = ctx.attention_tiles(ops.SIGMOID_ATTENTION_TILE_QUERIES, "all")
+        tiles, n = ctx.attention_tiles(ops.sigmoid_attention_tile_queries(H // G), "all")
         ops.sigmoid_attention(q, cache.k, cache.v, att, H, G, D, V, tiles, n, table, cache.page_tokens, s.scale,
                               self.head_bias, err=ctx.err, stream=ctx.stream)
         self.o(ctx, att, out, T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
