@@ -116,6 +116,8 @@ def cmd_info(args) -> int:
     print(cfg.describe())
     for elem, name in ((2, "bfloat16"), (4, "float32")):
         print(f"  KV cache per token, {name}: {cfg.kv_bytes_per_token(elem) / 1024:.1f} KiB")
+    if hasattr(cfg, "state_bytes_per_request"):
+        print(f"  state per request, float32: {cfg.state_bytes_per_request() / 1024:.1f} KiB")
     return 0
 
 

@@ -134,6 +134,21 @@ class FadosunConfig:
             d["max_positions"] = self.max_positions
         return d
 
+    def kv_bytes_per_token(self, elem_bytes: int) -> int:
+        """Bytes of paged cache one token takes: keys and values of the attention halves of the parallel layers."""
+        total = 0
+        for l in self.layers:
+            if l["type"] == "parallel":
+                a = l["mixer"]["left"]
+                total += a["kv_heads"] * (a["dim"] + a["vdim"]) * elem_bytes
+        return total
+
+    def state_bytes_per_request(self) -> int:
+        """Bytes of fixed-size fp32 state one request holds (matrices, normalisers, convolution inputs)."""
+        from ..cache.storage import state_bytes_per_request
+        from ..model.causal_lm import CausalLM
+        return state_bytes_per_request(CausalLM(self.to_model_spec()).cache_needs())
+
     def describe(self) -> str:
         kinds = ", ".join(l["type"] for l in self.layers[:8]) + (", ..." if len(self.layers) > 8 else "")
         return f"fadosun: {len(self.layers)} layers ({kinds}), width {self.width}, vocab {self.vocab}"

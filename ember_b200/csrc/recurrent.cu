@@ -353,7 +353,13 @@ struct ScanArgs {
     float* gates;                          // matrix memory: [T, H, 4]
 };
 
-template <int MODE, int RS>
+template <int N>
+struct TokenRegs {                                  // one token's vectors, scalars and column value, in registers
+    float4 v0[N], v1[N], v2[N], sc;
+    float val;
+};
+
+template <int MODE, int RS, int CT>
 __global__ void __launch_bounds__(RTHREADS) scan_chunks_kernel(ScanArgs p) {
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
@@ -361,7 +367,7 @@ __global__ void __launch_bounds__(RTHREADS) scan_chunks_kernel(ScanArgs p) {
     constexpr int NV = MODE == 0 ? 3 : 2;
     constexpr int VS = RG * (RS + 4);               // a vector in shared memory: row group r starts at r (RS + 4)
     constexpr int TOK = NV * VS + 4 + RCOLS;        // vectors, four scalars, the block's 32 column values
-    constexpr int CT = RS == 32 ? 8 : 16, TPW = CT / 8, EPL = RS / 4;
+    constexpr int TPW = (CT + 7) / 8, EPL = RS / 4;        // (CT: 16 or 8 tokens a chunk for prompt portions, 1 for decode steps)
     const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * RCOLS;
     const int D = p.D, V = p.V, H = p.H, grp = h / (H / p.G);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = lane & 7;
@@ -389,7 +395,7 @@ __global__ void __launch_bounds__(RTHREADS) scan_chunks_kernel(ScanArgs p) {
 #pragma unroll
         for (int w = 0; w < TPW; w++) {
             const int t = t0 + warp + 8 * w;
-            if (t >= end) continue;
+            if (warp + 8 * w >= CT || t >= end) continue;
             const float* row = p.x + (size_t)t * p.ld_x;
 #pragma unroll
             for (int m = 0; m < EPL; m++) {
@@ -409,7 +415,7 @@ __global__ void __launch_bounds__(RTHREADS) scan_chunks_kernel(ScanArgs p) {
 #pragma unroll
         for (int w = 0; w < TPW; w++) {
             const int tt = warp + 8 * w, t = t0 + tt;
-            if (t >= end) continue;
+            if (tt >= CT || t >= end) continue;
             float* tok = buf + tt * TOK;
             float s0 = 0.0f, s1 = 0.0f, s01 = 0.0f;
 #pragma unroll
@@ -456,55 +462,76 @@ __global__ void __launch_bounds__(RTHREADS) scan_chunks_kernel(ScanArgs p) {
         if (more) prefetch(t0 + CT);
         const int n = min(CT, end - t0);
         const float* buf = chunks + cur * CT * TOK;
-        for (int tt = 0; tt < n; tt++) {
+        // a token's operands are fetched into registers while the token before it is computed (two register sets,
+        // the loop unrolled by two), so that no multiply-add waits for shared memory
+        auto fetch = [&](int tt, TokenRegs<RS / 4>& x) {
             const float* tok = buf + tt * TOK;
-            const float4 sc = *reinterpret_cast<const float4*>(tok + NV * VS);
-            const float val = tok[NV * VS + 4 + cw];
-            const float4* v0 = reinterpret_cast<const float4*>(tok + base);
-            const float4* v1 = reinterpret_cast<const float4*>(tok + VS + base);
+            x.sc = *reinterpret_cast<const float4*>(tok + NV * VS);
+            x.val = tok[NV * VS + 4 + cw];
+#pragma unroll
+            for (int i4 = 0; i4 < RS / 4; i4++) {
+                x.v0[i4] = reinterpret_cast<const float4*>(tok + base)[i4];
+                x.v1[i4] = reinterpret_cast<const float4*>(tok + VS + base)[i4];
+                if (MODE == 0) x.v2[i4] = reinterpret_cast<const float4*>(tok + 2 * VS + base)[i4];
+            }
+        };
+        auto step = [&](int tt, const TokenRegs<RS / 4>& x) {
             float o;
             if (MODE == 0) {
-                const float4* v2 = reinterpret_cast<const float4*>(tok + 2 * VS + base);
-                float ak = 0.0f, aq = 0.0f;
+                float ak[4] = {0.0f, 0.0f, 0.0f, 0.0f}, aq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int i4 = 0; i4 < RS / 4; i4++) {
-                    const float4 k = v0[i4], q = v1[i4], g = v2[i4];
+                    const float4 k = x.v0[i4], q = x.v1[i4], g = x.v2[i4];
                     st[4 * i4 + 0] *= g.x; st[4 * i4 + 1] *= g.y; st[4 * i4 + 2] *= g.z; st[4 * i4 + 3] *= g.w;
-                    ak = fmaf(st[4 * i4 + 3], k.w, fmaf(st[4 * i4 + 2], k.z, fmaf(st[4 * i4 + 1], k.y, fmaf(st[4 * i4], k.x, ak))));
-                    aq = fmaf(st[4 * i4 + 3], q.w, fmaf(st[4 * i4 + 2], q.z, fmaf(st[4 * i4 + 1], q.y, fmaf(st[4 * i4], q.x, aq))));
+                    ak[0] = fmaf(st[4 * i4 + 0], k.x, ak[0]); ak[1] = fmaf(st[4 * i4 + 1], k.y, ak[1]);
+                    ak[2] = fmaf(st[4 * i4 + 2], k.z, ak[2]); ak[3] = fmaf(st[4 * i4 + 3], k.w, ak[3]);
+                    aq[0] = fmaf(st[4 * i4 + 0], q.x, aq[0]); aq[1] = fmaf(st[4 * i4 + 1], q.y, aq[1]);
+                    aq[2] = fmaf(st[4 * i4 + 2], q.z, aq[2]); aq[3] = fmaf(st[4 * i4 + 3], q.w, aq[3]);
                 }
+                float sk = (ak[0] + ak[1]) + (ak[2] + ak[3]), sq = (aq[0] + aq[1]) + (aq[2] + aq[3]);
 #pragma unroll
                 for (int off = 1; off < 8; off <<= 1) {
-                    ak += __shfl_xor_sync(0xffffffffu, ak, off);
-                    aq += __shfl_xor_sync(0xffffffffu, aq, off);
+                    sk += __shfl_xor_sync(0xffffffffu, sk, off);
+                    sq += __shfl_xor_sync(0xffffffffu, sq, off);
                 }
-                const float uk = sc.w * (val - ak * sc.x) * sc.x;              // beta (v - S^T k) / |k|
-                o = sc.y * fmaf(uk, sc.z, aq);
+                const float uk = x.sc.w * (x.val - sk * x.sc.x) * x.sc.x;      // beta (v - S^T k) / |k|
+                o = x.sc.y * fmaf(uk, x.sc.z, sq);
 #pragma unroll
                 for (int i4 = 0; i4 < RS / 4; i4++) {
-                    const float4 k = v0[i4];
+                    const float4 k = x.v0[i4];
                     st[4 * i4 + 0] = fmaf(k.x, uk, st[4 * i4 + 0]); st[4 * i4 + 1] = fmaf(k.y, uk, st[4 * i4 + 1]);
                     st[4 * i4 + 2] = fmaf(k.z, uk, st[4 * i4 + 2]); st[4 * i4 + 3] = fmaf(k.w, uk, st[4 * i4 + 3]);
                 }
             } else {
-                const float keep = sc.x, pv = sc.y * val;                       // put v | dt x
-                float acc = 0.0f;
+                const float keep = x.sc.x, pv = x.sc.y * x.val;                 // put v | dt x
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int i4 = 0; i4 < RS / 4; i4++) {
-                    const float4 k = v0[i4], q = v1[i4];
+                    const float4 k = x.v0[i4], q = x.v1[i4];
                     st[4 * i4 + 0] = fmaf(k.x, pv, keep * st[4 * i4 + 0]); st[4 * i4 + 1] = fmaf(k.y, pv, keep * st[4 * i4 + 1]);
                     st[4 * i4 + 2] = fmaf(k.z, pv, keep * st[4 * i4 + 2]); st[4 * i4 + 3] = fmaf(k.w, pv, keep * st[4 * i4 + 3]);
-                    acc = fmaf(st[4 * i4 + 3], q.w, fmaf(st[4 * i4 + 2], q.z, fmaf(st[4 * i4 + 1], q.y, fmaf(st[4 * i4], q.x, acc))));
+                    acc[0] = fmaf(st[4 * i4 + 0], q.x, acc[0]); acc[1] = fmaf(st[4 * i4 + 1], q.y, acc[1]);
+                    acc[2] = fmaf(st[4 * i4 + 2], q.z, acc[2]); acc[3] = fmaf(st[4 * i4 + 3], q.w, acc[3]);
                 }
-                o = rows_sum(acc);
-                if (MODE == 2) o = fmaf(skip, val, o);
+                o = rows_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+                if (MODE == 2) o = fmaf(skip, x.val, o);
             }
             if (live && r == 0) {
                 const int t = t0 + tt;
-                if (j < V) p.out[(size_t)t * H * V + h * V + j] = o;
+                if (j < V) __stcs(p.out + (size_t)t * H * V + h * V + j, o);
                 else p.gates[((size_t)t * H + h) * 4 + 3] = o;
             }
+        };
+        TokenRegs<RS / 4> A, B;
+        fetch(0, A);
+        int tt = 0;
+        for (; tt + 1 < n; tt += 2) {
+            fetch(tt + 1, B);
+            step(tt, A);
+            if (tt + 2 < n) fetch(tt + 2, A);
+            step(tt + 1, B);
         }
+        if (tt < n) step(tt, A);
         if (more) prepare(t0 + CT, chunks + (cur ^ 1) * CT * TOK);
         __syncthreads();
     }
@@ -518,24 +545,30 @@ inline bool regs_kernels_on() {
     return on != 0;
 }
 
-template <int MODE, int RS>
-inline int launch_scan_rs(const ScanArgs& p, int S, int n_cols, cudaStream_t st) {
-    constexpr int NV = MODE == 0 ? 3 : 2, CT = RS == 32 ? 8 : 16;
+template <int MODE, int RS, int CT>
+inline int launch_scan_ct(const ScanArgs& p, int S, int n_cols, cudaStream_t st) {
+    constexpr int NV = MODE == 0 ? 3 : 2;
     const size_t smem = ((size_t)RG * RS * 33 + 2 * CT * (NV * RG * (RS + 4) + 4 + RCOLS)) * sizeof(float);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(scan_chunks_kernel<MODE, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(scan_chunks_kernel<MODE, RS, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail("scan: %s", cudaGetErrorString(e));
     }
-    launch_kernel(scan_chunks_kernel<MODE, RS>, dim3(S, p.H, (n_cols + RCOLS - 1) / RCOLS), RTHREADS, smem, st, p);
+    launch_kernel(scan_chunks_kernel<MODE, RS, CT>, dim3(S, p.H, (n_cols + RCOLS - 1) / RCOLS), RTHREADS, smem, st, p);
     return 0;
 }
+// `single`: every run of the step is one token (a decode step): chunks of one token, small blocks, many per SM
+template <int MODE, int RS>
+inline int launch_scan_rs(const ScanArgs& p, int S, int n_cols, bool single, cudaStream_t st) {
+    if (single) return launch_scan_ct<MODE, RS, 1>(p, S, n_cols, st);
+    return launch_scan_ct<MODE, RS, (RS == 32 ? 8 : 16)>(p, S, n_cols, st);
+}
 template <int MODE>
-inline int launch_scan(const ScanArgs& p, int S, int n_cols, cudaStream_t st) {
+inline int launch_scan(const ScanArgs& p, int S, int n_cols, bool single, cudaStream_t st) {
     switch (rows_per_thread(p.D)) {
-        case 4: return launch_scan_rs<MODE, 4>(p, S, n_cols, st);
-        case 8: return launch_scan_rs<MODE, 8>(p, S, n_cols, st);
-        case 16: return launch_scan_rs<MODE, 16>(p, S, n_cols, st);
-        default: return launch_scan_rs<MODE, 32>(p, S, n_cols, st);
+        case 4: return launch_scan_rs<MODE, 4>(p, S, n_cols, single, st);
+        case 8: return launch_scan_rs<MODE, 8>(p, S, n_cols, single, st);
+        case 16: return launch_scan_rs<MODE, 16>(p, S, n_cols, single, st);
+        default: return launch_scan_rs<MODE, 32>(p, S, n_cols, single, st);
     }
 }
 
@@ -579,7 +612,7 @@ EMBER_API int ember_conv_silu(const float* x, int ldx, int c0, const float* taps
 
 EMBER_API int ember_delta_scan(const float* conv, int ld_conv, const float* beta, int ld_beta, const float* a, int ld_a,
                                const float* dt_bias, const float* A_log, float* state, long long state_stride, float* out,
-                               const int* query_start, const int* slots, int S, int H, int G, int D, int V, float key_eps,
+                               const int* query_start, const int* slots, int T, int S, int H, int G, int D, int V, float key_eps,
                                void* stream) {
     if (S <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0) return fail("delta_scan: %d/%d heads of %d x %d", H, G, D, V);
@@ -593,7 +626,7 @@ EMBER_API int ember_delta_scan(const float* conv, int ld_conv, const float* beta
         q.state = state; q.state_stride = state_stride; q.out = out; q.query_start = query_start; q.slots = slots;
         q.H = H; q.G = G; q.D = D; q.V = V; q.x = conv; q.ld_x = ld_conv; q.b = beta; q.ld_b = ld_beta; q.a = a; q.ld_a = ld_a;
         q.dt_bias = dt_bias; q.A_log = A_log; q.key_eps = key_eps;
-        if (launch_scan<0>(q, S, V, (cudaStream_t)stream)) return 1;
+        if (launch_scan<0>(q, S, V, T == S, (cudaStream_t)stream)) return 1;
         return check_launch("delta_scan");
     }
     launch_kernel(delta_scan_kernel, dim3(S, H, (V + VT - 1) / VT), VT, smem, (cudaStream_t)stream, p);
@@ -602,7 +635,7 @@ EMBER_API int ember_delta_scan(const float* conv, int ld_conv, const float* beta
 
 EMBER_API int ember_memory_scan(const float* proj, int ld, int off_q, int off_k, int off_v, int off_i, int off_f,
                                 const float* bias_i, const float* bias_f, float cap, float* state, long long state_stride,
-                                float* gates, float* out, const int* query_start, const int* slots, int S, int H, int D, int V,
+                                float* gates, float* out, const int* query_start, const int* slots, int T, int S, int H, int D, int V,
                                 void* stream) {
     if (S <= 0) return 0;
     if (H <= 0 || D <= 0 || V <= 0 || !(cap > 0.0f)) return fail("memory_scan: %d heads of %d x %d, cap %g", H, D, V, cap);
@@ -614,7 +647,7 @@ EMBER_API int ember_memory_scan(const float* proj, int ld, int off_q, int off_k,
         ScanArgs q{};
         q.state = state; q.state_stride = state_stride; q.out = out; q.query_start = query_start; q.slots = slots;
         q.H = H; q.G = H; q.D = D; q.V = V; q.x = proj; q.ld_x = ld; q.off_q = off_q; q.off_k = off_k; q.off_v = off_v; q.gates = gates;
-        if (launch_scan<1>(q, S, V + 1, st)) return 1;
+        if (launch_scan<1>(q, S, V + 1, T == S, st)) return 1;
         return check_launch("memory_scan");
     }
     size_t smem;
@@ -626,7 +659,7 @@ EMBER_API int ember_memory_scan(const float* proj, int ld, int off_q, int off_k,
 
 EMBER_API int ember_ssm_scan(const float* conv, int ld_conv, const float* dt, int ld_dt, const float* dt_bias, const float* A_log,
                              const float* skip, float* state, long long state_stride, float* out, const int* query_start,
-                             const int* slots, int S, int H, int G, int N, int V, void* stream) {
+                             const int* slots, int T, int S, int H, int G, int N, int V, void* stream) {
     if (S <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || N <= 0 || V <= 0) return fail("ssm_scan: %d heads in %d groups, state %d x %d", H, G, N, V);
     if (S > 65535 || H > 65535) return fail("ssm_scan: too many runs or heads for one launch");
@@ -639,7 +672,7 @@ EMBER_API int ember_ssm_scan(const float* conv, int ld_conv, const float* dt, in
         q.state = state; q.state_stride = state_stride; q.out = out; q.query_start = query_start; q.slots = slots;
         q.H = H; q.G = G; q.D = N; q.V = V; q.x = conv; q.ld_x = ld_conv; q.b = dt; q.ld_b = ld_dt; q.dt_bias = dt_bias;
         q.A_log = A_log; q.skip = skip;
-        if (launch_scan<2>(q, S, V, (cudaStream_t)stream)) return 1;
+        if (launch_scan<2>(q, S, V, T == S, (cudaStream_t)stream)) return 1;
         return check_launch("ssm_scan");
     }
     launch_kernel(ssm_scan_kernel, dim3(S, H, (V + VT - 1) / VT), VT, smem, (cudaStream_t)stream, p);

@@ -688,9 +688,9 @@ def conv_silu(x: torch.Tensor, col: int, taps: torch.Tensor, bias: Optional[torc
 
 def delta_scan(conv: torch.Tensor, beta: torch.Tensor, beta_col: int, a: torch.Tensor, a_col: int, dt_bias: torch.Tensor,
                A_log: torch.Tensor, state: torch.Tensor, out: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor,
-               S: int, heads: int, kv_heads: int, dim: int, vdim: int, key_eps: float, stream: Optional[int] = None) -> None:
+               T: int, S: int, heads: int, kv_heads: int, dim: int, vdim: int, key_eps: float, stream: Optional[int] = None) -> None:
     """Delta rule with a decay per head and key channel over the step's runs; the state [slots, >= heads dim vdim]
-    fp32 is read and left updated.  ``conv`` fp32 [T, q | k | v] after convolution and silu, ``beta`` logits at
+    fp32 is read and left updated (``T`` tokens in ``S`` runs; T == S, a decode step, takes small blocks).  ``conv`` fp32 [T, q | k | v] after convolution and silu, ``beta`` logits at
     column beta_col, decay logits at column a_col of ``a``; out fp32 [T, heads vdim]."""
     for t, n in ((conv, "conv"), (beta, "beta"), (a, "a"), (dt_bias, "dt_bias"), (A_log, "A_log"), (state, "state"), (out, "out")):
         _check(t, n, torch.float32)
@@ -702,12 +702,12 @@ def delta_scan(conv: torch.Tensor, beta: torch.Tensor, beta_col: int, a: torch.T
     lib = _lib("recurrent")
     _call(lib, lib.ember_delta_scan, _p(conv), c_int(conv.shape[1]), _off(beta, beta_col), c_int(beta.shape[1]), _off(a, a_col),
           c_int(a.shape[1]), _p(dt_bias), _p(A_log), _p(state), c_longlong(state.shape[1]), _p(out), _p(query_start), _p(slots),
-          c_int(S), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_float(key_eps), _stream(stream))
+          c_int(T), c_int(S), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_float(key_eps), _stream(stream))
 
 
 def memory_scan(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, off_i: int, off_f: int, bias_i: torch.Tensor,
                 bias_f: torch.Tensor, cap: float, state: torch.Tensor, gates: torch.Tensor, out: torch.Tensor,
-                query_start: torch.Tensor, slots: torch.Tensor, S: int, heads: int, dim: int, vdim: int,
+                query_start: torch.Tensor, slots: torch.Tensor, T: int, S: int, heads: int, dim: int, vdim: int,
                 stream: Optional[int] = None) -> None:
     """Matrix memory with exponential input gate and running maximum over the step's runs.  ``proj`` fp32 [T, ld]
     holds q, k, v and the two gates' logits at the given columns; the state row of a request is S [heads, dim, vdim],
@@ -722,11 +722,11 @@ def memory_scan(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, off_i: i
     lib = _lib("recurrent")
     _call(lib, lib.ember_memory_scan, _p(proj), c_int(proj.shape[1]), c_int(off_q), c_int(off_k), c_int(off_v), c_int(off_i),
           c_int(off_f), _p(bias_i), _p(bias_f), c_float(cap), _p(state), c_longlong(state.shape[1]), _p(gates), _p(out),
-          _p(query_start), _p(slots), c_int(S), c_int(heads), c_int(dim), c_int(vdim), _stream(stream))
+          _p(query_start), _p(slots), c_int(T), c_int(S), c_int(heads), c_int(dim), c_int(vdim), _stream(stream))
 
 
 def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, A_log: torch.Tensor, skip: torch.Tensor,
-             state: torch.Tensor, out: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor, S: int, heads: int,
+             state: torch.Tensor, out: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor, T: int, S: int, heads: int,
              groups: int, n_state: int, vdim: int, stream: Optional[int] = None) -> None:
     """Selective state space with a scalar decay per head over the step's runs.  ``conv`` fp32 [T, x | B | C] after
     convolution and silu, raw step sizes at column dt_col of ``dt``; state [slots, >= heads n_state vdim] fp32."""
@@ -738,7 +738,7 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, dt_col: int, dt_bias: torch.T
         raise KernelError("ssm_scan: buffers do not fit the head geometry")
     lib = _lib("recurrent")
     _call(lib, lib.ember_ssm_scan, _p(conv), c_int(conv.shape[1]), _off(dt, dt_col), c_int(dt.shape[1]), _p(dt_bias), _p(A_log),
-          _p(skip), _p(state), c_longlong(state.shape[1]), _p(out), _p(query_start), _p(slots), c_int(S), c_int(heads),
+          _p(skip), _p(state), c_longlong(state.shape[1]), _p(out), _p(query_start), _p(slots), c_int(T), c_int(S), c_int(heads),
           c_int(groups), c_int(n_state), c_int(vdim), _stream(stream))
 
 

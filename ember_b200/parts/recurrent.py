@@ -124,7 +124,7 @@ class GatedDelta(_StateMixer):
         ops.conv_silu(proj, 0, self.taps, None, cache.state, H * D * V, ctx.seq_of, ctx.query_start, ctx.state_slots, conv,
                       T, ctx.S, stream=ctx.stream)
         ops.delta_scan(conv, proj, C, ag, 0, self.dt_bias, self.A_log, cache.state, o, ctx.query_start, ctx.state_slots,
-                       ctx.S, H, s.num_kv_heads, D, V, s.key_eps, stream=ctx.stream)
+                       T, ctx.S, H, s.num_kv_heads, D, V, s.key_eps, stream=ctx.stream)
         ops.group_norm_gate(o, 0, ag, H * D, self.norm_w, False, s.norm_eps, ops.GATE_SIGMOID_AFTER, y, T, H, V,
                             stream=ctx.stream)
         self._out(ctx, y, out, accumulate)
@@ -182,7 +182,7 @@ class MatrixMemory(_StateMixer):
         y = ctx.buf("mlstm.normed", (mt, self.vd), rt.dtype)
         self.in_proj(ctx, x, proj, T, ops.EPI_STORE_F32)
         ops.memory_scan(proj, 0, off_k, off_v, off_i, off_i + H, self.bias_i, self.bias_f, s.gate_cap, cache.state, gates, o,
-                        ctx.query_start, ctx.state_slots, ctx.S, H, D, V, stream=ctx.stream)
+                        ctx.query_start, ctx.state_slots, T, ctx.S, H, D, V, stream=ctx.stream)
         ops.group_norm_gate(o, 0, proj, off_g, self.norm_w, True, s.norm_eps, ops.GATE_SIGMOID_AFTER, y, T, H, V, den=gates,
                             stream=ctx.stream)
         self._out(ctx, y, out, accumulate)
@@ -243,7 +243,7 @@ class StateSpace(_StateMixer):
         ops.conv_silu(proj, inner, self.taps, self.conv_bias, cache.state, H * N * V, ctx.seq_of, ctx.query_start,
                       ctx.state_slots, conv, T, ctx.S, stream=ctx.stream)
         ops.ssm_scan(conv, proj, inner + C, self.dt_bias, self.A_log, self.skip, cache.state, o, ctx.query_start,
-                     ctx.state_slots, ctx.S, H, s.num_groups, N, V, stream=ctx.stream)
+                     ctx.state_slots, T, ctx.S, H, s.num_groups, N, V, stream=ctx.stream)
         ops.group_norm_gate(o, 0, proj, 0, self.norm_w, True, s.norm_eps, ops.GATE_SILU_BEFORE, y, T, s.norm_groups,
                             inner // s.norm_groups, stream=ctx.stream)
         self._out(ctx, y, out, accumulate)

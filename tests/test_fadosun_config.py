@@ -75,3 +75,18 @@ def test_plain_recurrences_do_not_look_ahead(tmp_path):
     toks = torch.randint(0, 257, (23,), generator=torch.Generator().manual_seed(3)).tolist()
     whole = plain.forward(cfg, W, toks)
     assert torch.allclose(plain.forward(cfg, W, toks[:9]), whole[:9], atol=1e-10)
+
+
+def test_command_line_random_then_info(tmp_path, capsys):
+    from ember_b200.cli import main
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(FADOSUN["p"]["json"]))
+    out = tmp_path / "model"
+    assert main(["random", "--config", str(cfg), "--out", str(out), "--seed", "3"]) == 0
+    assert sorted(os.listdir(out)) == ["config.json", "model.safetensors"]
+    capsys.readouterr()
+    assert main(["info", "-m", str(out)]) == 0
+    text = capsys.readouterr().out
+    assert "fadosun" in text and "3 layers" in text and "state per request" in text
+    # keys and values of the one attention layer: 2 key heads of 32 + 24, bfloat16
+    assert "KV cache per token, bfloat16: 0.2 KiB" in text
