@@ -360,7 +360,7 @@ struct TokenRegs {                                  // one token's vectors, scal
 };
 
 template <int MODE, int RS, int CT>
-__global__ void __launch_bounds__(RTHREADS) scan_chunks_kernel(ScanArgs p) {
+__global__ void __launch_bounds__(RTHREADS, CT == 1 ? 3 : 1) scan_chunks_kernel(ScanArgs p) {
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -381,7 +381,6 @@ __global__ void __launch_bounds__(RTHREADS) scan_chunks_kernel(ScanArgs p) {
     float* extra = MODE == 1 ? sbase + (size_t)H * D * V + (size_t)h * D : nullptr;
     float st[RS];
     for (int i = threadIdx.x; i < 2 * CT * TOK; i += RTHREADS) chunks[i] = 0.0f;
-    regs_load<RS>(st, tile, S, D, V, col0, extra);
     const int first = p.query_start[s], end = p.query_start[s + 1];
     const float rate = MODE == 1 ? 0.0f : expf(p.A_log[h]);
     const float qscale = 1.0f / sqrtf((float)D);
@@ -453,7 +452,8 @@ __global__ void __launch_bounds__(RTHREADS) scan_chunks_kernel(ScanArgs p) {
     };
 
     const float skip = MODE == 2 ? p.skip[h] : 0.0f;
-    prefetch(first);
+    prefetch(first);                                // (before the state: both trips to global memory overlap)
+    regs_load<RS>(st, tile, S, D, V, col0, extra);
     prepare(first, chunks);
     __syncthreads();
     int cur = 0;

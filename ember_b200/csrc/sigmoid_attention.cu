@@ -202,6 +202,199 @@ inline int heads_per_block(int group) {
     return h;
 }
 
+// ------------------------------------------------------------------------ bfloat16 cache: tensor-core tiles
+// The same attention for bfloat16 queries and cache with head sizes the tiles take (D a multiple of 16, V of 32).
+// q . k runs on the tensor cores (mma.sync m16n8k16, bf16 operands, fp32 accumulation: what the fp32 multiply-adds
+// of the kernel above compute from the same bf16 values).  Scores, sigmoid and weights are fp32; for the weight x
+// value product a weight is cut into three bf16 pieces p = p1 + p2 + p3 (24 bits of mantissa: the fp32 weight, not a
+// rounded one) and the three products are added in the fp32 accumulator.  A block: 16 (token, head) rows, 64-key
+// tiles fetched with cp.async into two buffers; warp w takes keys 16 w .. 16 w + 15 of a tile for the scores and a
+// quarter of the value columns for the read-out; the weights pass through shared memory.
+constexpr int TC_KEYS = 64;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// the three bf16 pieces of two fp32 weights, packed pairwise
+__device__ __forceinline__ void split3(float x, float y, uint32_t& p1, uint32_t& p2, uint32_t& p3) {
+    const float x1 = __bfloat162float(__float2bfloat16_rn(x)), y1 = __bfloat162float(__float2bfloat16_rn(y));
+    const float xr = x - x1, yr = y - y1;
+    const float x2 = __bfloat162float(__float2bfloat16_rn(xr)), y2 = __bfloat162float(__float2bfloat16_rn(yr));
+    p1 = pack_bf16(x1, y1); p2 = pack_bf16(x2, y2); p3 = pack_bf16(xr - x2, yr - y2);
+}
+
+template <int DK, int NBV>          // DK: most 16-element steps of a head (D <= 16 DK); NBV: most 8-column blocks a warp reads out
+__global__ void __launch_bounds__(128)
+sigmoid_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                            const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, int H, int G, int D,
+                            int V, int hpb, const int* __restrict__ tiles, const int* __restrict__ block_table, int max_blocks,
+                            int page, int num_pages, float scale, const float* __restrict__ head_bias, int* __restrict__ err) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int* tile = tiles + 4 * blockIdx.x;
+    const int run = tile[0], row0 = tile[1], nq = tile[2], pos0 = tile[3];
+    const int h0 = blockIdx.y * hpb, kv = h0 / (H / G);
+    const int n_rows = nq * hpb;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
+    const int DP = D + 8, VP = V + 8, PP = TC_KEYS + 8;            // row pitches in elements
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [2][64][DP]
+    __nv_bfloat16* Vs = Ks + 2 * TC_KEYS * DP;                                      // [2][64][VP]
+    __nv_bfloat16* Ps = Vs + 2 * TC_KEYS * VP;                                      // [3][16][PP]
+    const int dk = D >> 4, vw = V >> 2, nbv = vw >> 3;              // steps of 16, columns and 8-column blocks per warp
+    const int n_keys = pos0 + nq;
+    const int* bt = block_table + (size_t)run * max_blocks;
+
+    auto fetch = [&](int k0, int buf) {
+        const int dch = D >> 3, vch = V >> 3;                      // 16-byte chunks a row
+        for (int e = threadIdx.x; e < TC_KEYS * (dch + vch); e += 128) {
+            const int r = e / (dch + vch), ch = e - r * (dch + vch), kp = k0 + r;
+            const bool is_k = ch < dch;
+            __nv_bfloat16* dst = is_k ? Ks + ((size_t)buf * TC_KEYS + r) * DP + 8 * ch
+                                      : Vs + ((size_t)buf * TC_KEYS + r) * VP + 8 * (ch - dch);
+            const int blk = kp < n_keys ? bt[kp / page] : -1;
+            if (blk >= 0 && blk < num_pages) {
+                const __nv_bfloat16* src = is_k ? k_pool + (((size_t)blk * G + kv) * page + kp % page) * D + 8 * ch
+                                                : v_pool + (((size_t)blk * G + kv) * page + kp % page) * V + 8 * (ch - dch);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+            } else {
+                if (kp < n_keys && err) atomicOr(err, EMBER_ERR_PAGE_RANGE);
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+
+    // the queries of rows g and g + 8 as A operands, kept for the whole key range
+    uint32_t qa[DK][4];
+    {
+        const int r0 = g, r1 = g + 8;
+        const __nv_bfloat16* q0 = q + ((size_t)(row0 + r0 / hpb) * H + h0 + r0 % hpb) * D;
+        const __nv_bfloat16* q1 = q + ((size_t)(row0 + r1 / hpb) * H + h0 + r1 % hpb) * D;
+#pragma unroll
+        for (int ks = 0; ks < DK; ks++) {
+            if (ks < dk) {
+                qa[ks][0] = r0 < n_rows ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * c) : 0u;
+                qa[ks][1] = r1 < n_rows ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * c) : 0u;
+                qa[ks][2] = r0 < n_rows ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * c) : 0u;
+                qa[ks][3] = r1 < n_rows ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * c) : 0u;
+            }
+        }
+    }
+    const float bias0 = (head_bias && g < n_rows) ? head_bias[h0 + g % hpb] : 0.0f;
+    const float bias1 = (head_bias && g + 8 < n_rows) ? head_bias[h0 + (g + 8) % hpb] : 0.0f;
+    const int qpos0 = pos0 + g / hpb, qpos1 = pos0 + (g + 8) / hpb;
+    float acc[NBV][4];
+#pragma unroll
+    for (int nb = 0; nb < NBV; nb++) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.0f;
+
+    fetch(0, 0);
+    int buf = 0;
+    for (int k0 = 0; k0 < n_keys; k0 += TC_KEYS, buf ^= 1) {
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();                                            // the tile is in; the other buffer and P are free
+        if (k0 + TC_KEYS < n_keys) fetch(k0 + TC_KEYS, buf ^ 1);
+        const __nv_bfloat16* Kt = Ks + (size_t)buf * TC_KEYS * DP;
+        const __nv_bfloat16* Vt = Vs + (size_t)buf * TC_KEYS * VP;
+        // scores of this warp's 16 keys, their weights in three pieces to shared memory
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++) {
+            float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const __nv_bfloat16* krow = Kt + (size_t)(16 * warp + 8 * nb + g) * DP + 2 * c;
+#pragma unroll
+            for (int ks = 0; ks < DK; ks++) {
+                if (ks < dk) {
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
+                    mma_bf16_16816(sc, qa[ks], b0, b1);
+                }
+            }
+            const int key = k0 + 16 * warp + 8 * nb + 2 * c;        // this thread's columns: key, key + 1
+            float w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int kp = key + (i & 1), qp = i < 2 ? qpos0 : qpos1;
+                const bool seen = (i < 2 ? g : g + 8) < n_rows && kp <= qp;
+                w[i] = seen ? 1.0f / (1.0f + expf(-(sc[i] * scale + (i < 2 ? bias0 : bias1)))) : 0.0f;
+            }
+            uint32_t p1, p2, p3;
+            const int col = 16 * warp + 8 * nb + 2 * c;
+            split3(w[0], w[1], p1, p2, p3);
+            *reinterpret_cast<uint32_t*>(Ps + (0 * 16 + g) * PP + col) = p1;
+            *reinterpret_cast<uint32_t*>(Ps + (1 * 16 + g) * PP + col) = p2;
+            *reinterpret_cast<uint32_t*>(Ps + (2 * 16 + g) * PP + col) = p3;
+            split3(w[2], w[3], p1, p2, p3);
+            *reinterpret_cast<uint32_t*>(Ps + (0 * 16 + g + 8) * PP + col) = p1;
+            *reinterpret_cast<uint32_t*>(Ps + (1 * 16 + g + 8) * PP + col) = p2;
+            *reinterpret_cast<uint32_t*>(Ps + (2 * 16 + g + 8) * PP + col) = p3;
+        }
+        __syncthreads();
+        // read-out of this warp's value columns
+        const int kbs = min(TC_KEYS, n_keys - k0 + 15) >> 4;        // 16-key steps that hold a visible key
+#pragma unroll
+        for (int kb = 0; kb < TC_KEYS / 16; kb++) {
+            if (kb < kbs) {
+                uint32_t pa[3][4];
+#pragma unroll
+                for (int part = 0; part < 3; part++) {
+                    const __nv_bfloat16* pr = Ps + (size_t)(part * 16 + g) * PP + kb * 16 + 2 * c;
+                    pa[part][0] = *reinterpret_cast<const uint32_t*>(pr);
+                    pa[part][1] = *reinterpret_cast<const uint32_t*>(pr + 8 * PP);
+                    pa[part][2] = *reinterpret_cast<const uint32_t*>(pr + 8);
+                    pa[part][3] = *reinterpret_cast<const uint32_t*>(pr + 8 * PP + 8);
+                }
+#pragma unroll
+                for (int nb = 0; nb < NBV; nb++) {
+                    if (nb < nbv) {
+                        uint32_t b0, b1;
+                        const __nv_bfloat16* vrow = Vt + (size_t)(kb * 16 + (lane & 15)) * VP + warp * vw + nb * 8;
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
+                                     : "=r"(b0), "=r"(b1) : "r"((uint32_t)__cvta_generic_to_shared(vrow)));
+                        mma_bf16_16816(acc[nb], pa[2], b0, b1);     // smallest pieces first
+                        mma_bf16_16816(acc[nb], pa[1], b0, b1);
+                        mma_bf16_16816(acc[nb], pa[0], b0, b1);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int nb = 0; nb < NBV; nb++) {
+        if (nb < nbv) {
+            const int col = warp * vw + nb * 8 + 2 * c;
+            if (g < n_rows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + g / hpb) * H + h0 + g % hpb) * V + col) = pack_bf16(acc[nb][0], acc[nb][1]);
+            if (g + 8 < n_rows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + (g + 8) / hpb) * H + h0 + (g + 8) % hpb) * V + col) =
+                    pack_bf16(acc[nb][2], acc[nb][3]);
+        }
+    }
+}
+
+inline bool tc_attend_on() {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("EMBER_SIGMOID_ATTENTION_TC"); on = (e && e[0] == '0') ? 0 : 1; }
+    return on != 0;
+}
+
+template <int DK, int NBV>
+int launch_attend_tc(const void* q, const void* k_pool, const void* v_pool, void* out, int H, int G, int D, int V, int hpb,
+                     const int* tiles, int n_tiles, const int* bt, int max_blocks, int page, int num_pages, float scale,
+                     const float* head_bias, int* err, cudaStream_t st) {
+    const size_t smem = ((size_t)2 * TC_KEYS * (D + 8) + (size_t)2 * TC_KEYS * (V + 8) + 3 * 16 * (TC_KEYS + 8)) * sizeof(__nv_bfloat16);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(sigmoid_attention_tc_kernel<DK, NBV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(sigmoid_attention_tc_kernel<DK, NBV>, dim3(n_tiles, H / hpb), 128, smem, st, (const __nv_bfloat16*)q,
+                  (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, H, G, D, V, hpb, tiles, bt, max_blocks,
+                  page, num_pages, scale, head_bias, err);
+    return check_launch("sigmoid_attention");
+}
+
 template <typename T>
 int launch_attend(const void* q, const void* k_pool, const void* v_pool, void* out, int H, int G, int D, int V,
                   const int* tiles, int n_tiles, const int* bt, int max_blocks, int page, int num_pages, float scale,
@@ -262,6 +455,14 @@ EMBER_API int ember_sigmoid_attention(const void* q, const void* k_pool, const v
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == EMBER_F32)
         return launch_attend<float>(q, k_pool, v_pool, out, H, G, D, V, tiles, n_tiles, block_table, max_blocks, page, num_pages, scale, head_bias, err, st);
+    if (dtype == EMBER_BF16 && tc_attend_on() && D % 16 == 0 && V % 32 == 0 && D <= 256 && V <= 512) {
+        const int hpb = heads_per_block(H / G);
+#define EMBER_SA_TC(DK, NBV) launch_attend_tc<DK, NBV>(q, k_pool, v_pool, out, H, G, D, V, hpb, tiles, n_tiles, block_table, \
+                                                       max_blocks, page, num_pages, scale, head_bias, err, st)
+        if (D <= 128) return V <= 128 ? EMBER_SA_TC(8, 4) : EMBER_SA_TC(8, 16);
+        return V <= 128 ? EMBER_SA_TC(16, 4) : EMBER_SA_TC(16, 16);
+#undef EMBER_SA_TC
+    }
     if (dtype == EMBER_BF16)
         return launch_attend<__nv_bfloat16>(q, k_pool, v_pool, out, H, G, D, V, tiles, n_tiles, block_table, max_blocks, page, num_pages, scale, head_bias, err, st);
     return fail("sigmoid_attention: unsupported dtype %d", dtype);
