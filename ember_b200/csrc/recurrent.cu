@@ -292,45 +292,56 @@ __global__ void ssm_scan_kernel(SsmArgs p) {
 }
 
 // ------------------------------------------------------------------ the same recurrences, state in registers
-// For up to 256 state rows a block of 256 threads takes 32 value columns: lane = row group r (8 of them) + 8 x column
-// (4 per warp), and a thread keeps rows r RS .. r RS + RS - 1 of its column in registers.  A dot product over the rows
-// is RS multiply-adds and three shuffles; the per-token vectors live in shared memory, one padding word per row
+// For up to 256 state rows a block takes 32 value columns: lane = row group r (RG = 8 or 16 of them) + RG x column,
+// and a thread keeps rows r RS .. r RS + RS - 1 of its column in registers.  A dot product over the rows
+// is RS multiply-adds and log2(RG) shuffles; the per-token vectors live in shared memory, one padding word per row
 // group so that the eight groups read eight banks.  The state goes through a shared tile when it is loaded and
 // stored, so that global memory sees whole 128-byte rows.  A prompt portion of one request keeps 8 times the threads
 // of the kernels above busy; those stay for more than 256 rows.
-constexpr int RG = 8, RCOLS = 32, RTHREADS = 256;
+constexpr int RCOLS = 32;
 
-template <int RS>
+// RG row groups (8 or 16 lanes of a warp share a column), RS rows a thread, 32 RG threads a block.  The state goes
+// through a shared tile: every thread first fetches RS values of whole 128-byte rows (all loads in flight together).
+template <int RS, int RG>
 __device__ __forceinline__ void regs_load(float (&st)[RS], float* tile, const float* __restrict__ S, int D, int V, int col0,
                                           const float* __restrict__ extra = nullptr) {
-    const int c = threadIdx.x & 31;
-    for (int i = threadIdx.x >> 5; i < RG * RS; i += RTHREADS / 32)
-        tile[i * 33 + c] = (i < D && col0 + c < V) ? S[(size_t)i * V + col0 + c]
-                                                   : ((extra && i < D && col0 + c == V) ? extra[i] : 0.0f);
+    const int c = threadIdx.x & 31, w = threadIdx.x >> 5;
+    float tmp[RS];
+#pragma unroll
+    for (int k = 0; k < RS; k++) {
+        const int i = w + RG * k;                      // (RG warps a block: rows w, w + RG, ...)
+        tmp[k] = (i < D && col0 + c < V) ? S[(size_t)i * V + col0 + c]
+                                         : ((extra && i < D && col0 + c == V) ? extra[i] : 0.0f);
+    }
+#pragma unroll
+    for (int k = 0; k < RS; k++) tile[(w + RG * k) * 33 + c] = tmp[k];
     __syncthreads();
-    const int lane = threadIdx.x & 31, r = lane & 7, cc = (threadIdx.x >> 5) * 4 + (lane >> 3);
+    const int lane = threadIdx.x & 31, r = lane % RG, cc = w * (32 / RG) + lane / RG;
 #pragma unroll
     for (int ii = 0; ii < RS; ii++) st[ii] = tile[(r * RS + ii) * 33 + cc];
 }
-template <int RS>
+template <int RS, int RG>
 __device__ __forceinline__ void regs_store(const float (&st)[RS], float* tile, float* __restrict__ S, int D, int V, int col0,
                                            float* __restrict__ extra = nullptr) {
-    const int lane = threadIdx.x & 31, r = lane & 7, cc = (threadIdx.x >> 5) * 4 + (lane >> 3);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, r = lane % RG, cc = w * (32 / RG) + lane / RG;
     __syncthreads();
 #pragma unroll
     for (int ii = 0; ii < RS; ii++) tile[(r * RS + ii) * 33 + cc] = st[ii];
     __syncthreads();
-    const int c = threadIdx.x & 31;
-    for (int i = threadIdx.x >> 5; i < RG * RS; i += RTHREADS / 32)
+    const int c = lane;
+#pragma unroll
+    for (int k = 0; k < RS; k++) {
+        const int i = w + RG * k;
         if (i < D) {
             if (col0 + c < V) S[(size_t)i * V + col0 + c] = tile[i * 33 + c];
             else if (extra && col0 + c == V) extra[i] = tile[i * 33 + c];
         }
+    }
 }
+template <int RG>
 __device__ __forceinline__ float rows_sum(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
+#pragma unroll
+    for (int off = 1; off < RG; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
     return v;
 }
 
@@ -359,19 +370,20 @@ struct TokenRegs {                                  // one token's vectors, scal
     float val;
 };
 
-template <int MODE, int RS, int CT>
-__global__ void __launch_bounds__(RTHREADS, CT == 1 ? 3 : 1) scan_chunks_kernel(ScanArgs p) {
+template <int MODE, int RS, int CT, int RG>
+__global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(ScanArgs p) {
+    constexpr int RTHREADS = 32 * RG, NW = RG;      // warps a block: 32 columns, 32 / RG of them a warp
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
     pdl_wait();
     constexpr int NV = MODE == 0 ? 3 : 2;
     constexpr int VS = RG * (RS + 4);               // a vector in shared memory: row group r starts at r (RS + 4)
     constexpr int TOK = NV * VS + 4 + RCOLS;        // vectors, four scalars, the block's 32 column values
-    constexpr int TPW = (CT + 7) / 8, EPL = RS / 4;        // (CT: 16 or 8 tokens a chunk for prompt portions, 1 for decode steps)
+    constexpr int TPW = (CT + NW - 1) / NW, EPL = RG * RS / 32;   // (CT: 16 or 8 tokens a chunk for prompt portions, 1 for decode steps)
     const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * RCOLS;
     const int D = p.D, V = p.V, H = p.H, grp = h / (H / p.G);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = lane & 7;
-    const int cw = warp * 4 + (lane >> 3), j = col0 + cw, base = r * (RS + 4);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = lane % RG;
+    const int cw = warp * (32 / RG) + lane / RG, j = col0 + cw, base = r * (RS + 4);
     const int n_cols = MODE == 1 ? V + 1 : V;       // (matrix memory: column V is n)
     const bool live = j < n_cols;
     float* tile = smem;                             // [RG RS][33], used when the state is loaded and stored
@@ -393,8 +405,8 @@ __global__ void __launch_bounds__(RTHREADS, CT == 1 ? 3 : 1) scan_chunks_kernel(
     auto prefetch = [&](int t0) {
 #pragma unroll
         for (int w = 0; w < TPW; w++) {
-            const int t = t0 + warp + 8 * w;
-            if (warp + 8 * w >= CT || t >= end) continue;
+            const int t = t0 + warp + NW * w;
+            if (warp + NW * w >= CT || t >= end) continue;
             const float* row = p.x + (size_t)t * p.ld_x;
 #pragma unroll
             for (int m = 0; m < EPL; m++) {
@@ -413,7 +425,7 @@ __global__ void __launch_bounds__(RTHREADS, CT == 1 ? 3 : 1) scan_chunks_kernel(
     auto prepare = [&](int t0, float* buf) {
 #pragma unroll
         for (int w = 0; w < TPW; w++) {
-            const int tt = warp + 8 * w, t = t0 + tt;
+            const int tt = warp + NW * w, t = t0 + tt;
             if (tt >= CT || t >= end) continue;
             float* tok = buf + tt * TOK;
             float s0 = 0.0f, s1 = 0.0f, s01 = 0.0f;
@@ -453,7 +465,7 @@ __global__ void __launch_bounds__(RTHREADS, CT == 1 ? 3 : 1) scan_chunks_kernel(
 
     const float skip = MODE == 2 ? p.skip[h] : 0.0f;
     prefetch(first);                                // (before the state: both trips to global memory overlap)
-    regs_load<RS>(st, tile, S, D, V, col0, extra);
+    regs_load<RS, RG>(st, tile, S, D, V, col0, extra);
     prepare(first, chunks);
     __syncthreads();
     int cur = 0;
@@ -490,7 +502,7 @@ __global__ void __launch_bounds__(RTHREADS, CT == 1 ? 3 : 1) scan_chunks_kernel(
                 }
                 float sk = (ak[0] + ak[1]) + (ak[2] + ak[3]), sq = (aq[0] + aq[1]) + (aq[2] + aq[3]);
 #pragma unroll
-                for (int off = 1; off < 8; off <<= 1) {
+                for (int off = 1; off < RG; off <<= 1) {
                     sk += __shfl_xor_sync(0xffffffffu, sk, off);
                     sq += __shfl_xor_sync(0xffffffffu, sq, off);
                 }
@@ -513,7 +525,7 @@ __global__ void __launch_bounds__(RTHREADS, CT == 1 ? 3 : 1) scan_chunks_kernel(
                     acc[0] = fmaf(st[4 * i4 + 0], q.x, acc[0]); acc[1] = fmaf(st[4 * i4 + 1], q.y, acc[1]);
                     acc[2] = fmaf(st[4 * i4 + 2], q.z, acc[2]); acc[3] = fmaf(st[4 * i4 + 3], q.w, acc[3]);
                 }
-                o = rows_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+                o = rows_sum<RG>((acc[0] + acc[1]) + (acc[2] + acc[3]));
                 if (MODE == 2) o = fmaf(skip, x.val, o);
             }
             if (live && r == 0) {
@@ -535,7 +547,7 @@ __global__ void __launch_bounds__(RTHREADS, CT == 1 ? 3 : 1) scan_chunks_kernel(
         if (more) prepare(t0 + CT, chunks + (cur ^ 1) * CT * TOK);
         __syncthreads();
     }
-    regs_store<RS>(st, tile, S, D, V, col0, extra);
+    regs_store<RS, RG>(st, tile, S, D, V, col0, extra);
 }
 
 inline int rows_per_thread(int D) { return D <= 32 ? 4 : (D <= 64 ? 8 : (D <= 128 ? 16 : (D <= 256 ? 32 : 0))); }
@@ -545,30 +557,28 @@ inline bool regs_kernels_on() {
     return on != 0;
 }
 
-template <int MODE, int RS, int CT>
+template <int MODE, int RS, int CT, int RG>
 inline int launch_scan_ct(const ScanArgs& p, int S, int n_cols, cudaStream_t st) {
     constexpr int NV = MODE == 0 ? 3 : 2;
     const size_t smem = ((size_t)RG * RS * 33 + 2 * CT * (NV * RG * (RS + 4) + 4 + RCOLS)) * sizeof(float);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(scan_chunks_kernel<MODE, RS, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(scan_chunks_kernel<MODE, RS, CT, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail("scan: %s", cudaGetErrorString(e));
     }
-    launch_kernel(scan_chunks_kernel<MODE, RS, CT>, dim3(S, p.H, (n_cols + RCOLS - 1) / RCOLS), RTHREADS, smem, st, p);
+    launch_kernel(scan_chunks_kernel<MODE, RS, CT, RG>, dim3(S, p.H, (n_cols + RCOLS - 1) / RCOLS), 32 * RG, smem, st, p);
     return 0;
 }
-// `single`: every run of the step is one token (a decode step): chunks of one token, small blocks, many per SM
-template <int MODE, int RS>
-inline int launch_scan_rs(const ScanArgs& p, int S, int n_cols, bool single, cudaStream_t st) {
-    if (single) return launch_scan_ct<MODE, RS, 1>(p, S, n_cols, st);
-    return launch_scan_ct<MODE, RS, (RS == 32 ? 8 : 16)>(p, S, n_cols, st);
-}
+// `single`: every run of the step is one token (a decode step): chunks of one token, small blocks, several per SM
+// (the step is bound by the state's bytes).  Eight lanes a column in both cases: sixteen (half the rows a thread, one
+// more shuffle) were measured equal for prompt portions (6.49 against 6.34 ms for the eight scans of a 2,048-token
+// step at heads of 128), so the kernel keeps the parameter and the launcher one choice.
 template <int MODE>
 inline int launch_scan(const ScanArgs& p, int S, int n_cols, bool single, cudaStream_t st) {
     switch (rows_per_thread(p.D)) {
-        case 4: return launch_scan_rs<MODE, 4>(p, S, n_cols, single, st);
-        case 8: return launch_scan_rs<MODE, 8>(p, S, n_cols, single, st);
-        case 16: return launch_scan_rs<MODE, 16>(p, S, n_cols, single, st);
-        default: return launch_scan_rs<MODE, 32>(p, S, n_cols, single, st);
+        case 4: return single ? launch_scan_ct<MODE, 4, 1, 8>(p, S, n_cols, st) : launch_scan_ct<MODE, 4, 16, 8>(p, S, n_cols, st);
+        case 8: return single ? launch_scan_ct<MODE, 8, 1, 8>(p, S, n_cols, st) : launch_scan_ct<MODE, 8, 16, 8>(p, S, n_cols, st);
+        case 16: return single ? launch_scan_ct<MODE, 16, 1, 8>(p, S, n_cols, st) : launch_scan_ct<MODE, 16, 16, 8>(p, S, n_cols, st);
+        default: return single ? launch_scan_ct<MODE, 32, 1, 8>(p, S, n_cols, st) : launch_scan_ct<MODE, 32, 8, 8>(p, S, n_cols, st);
     }
 }
 

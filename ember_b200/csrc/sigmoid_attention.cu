@@ -251,20 +251,25 @@ sigmoid_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const int n_keys = pos0 + nq;
     const int* bt = block_table + (size_t)run * max_blocks;
 
+    // a thread fetches pieces of one key row (two threads a row, 32 bytes side by side): one look at the block table
     auto fetch = [&](int k0, int buf) {
-        const int dch = D >> 3, vch = V >> 3;                      // 16-byte chunks a row
-        for (int e = threadIdx.x; e < TC_KEYS * (dch + vch); e += 128) {
-            const int r = e / (dch + vch), ch = e - r * (dch + vch), kp = k0 + r;
+        const int dch = D >> 3, vch = V >> 3;                      // 16-byte chunks a row (both even)
+        const int r = threadIdx.x >> 1, kp = k0 + r;
+        const int blk = kp < n_keys ? bt[kp / page] : -1;
+        const bool ok = blk >= 0 && blk < num_pages;
+        if (!ok && kp < n_keys && err && (threadIdx.x & 1) == 0) atomicOr(err, EMBER_ERR_PAGE_RANGE);
+        const size_t at = ok ? ((size_t)blk * G + kv) * page + kp % page : 0;
+        const __nv_bfloat16* ksrc = k_pool + at * D;
+        const __nv_bfloat16* vsrc = v_pool + at * V;
+        __nv_bfloat16* kdst = Ks + ((size_t)buf * TC_KEYS + r) * DP;
+        __nv_bfloat16* vdst = Vs + ((size_t)buf * TC_KEYS + r) * VP;
+        for (int ch = threadIdx.x & 1; ch < dch + vch; ch += 2) {
             const bool is_k = ch < dch;
-            __nv_bfloat16* dst = is_k ? Ks + ((size_t)buf * TC_KEYS + r) * DP + 8 * ch
-                                      : Vs + ((size_t)buf * TC_KEYS + r) * VP + 8 * (ch - dch);
-            const int blk = kp < n_keys ? bt[kp / page] : -1;
-            if (blk >= 0 && blk < num_pages) {
-                const __nv_bfloat16* src = is_k ? k_pool + (((size_t)blk * G + kv) * page + kp % page) * D + 8 * ch
-                                                : v_pool + (((size_t)blk * G + kv) * page + kp % page) * V + 8 * (ch - dch);
+            __nv_bfloat16* dst = is_k ? kdst + 8 * ch : vdst + 8 * (ch - dch);
+            if (ok) {
+                const __nv_bfloat16* src = is_k ? ksrc + 8 * ch : vsrc + 8 * (ch - dch);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
             } else {
-                if (kp < n_keys && err) atomicOr(err, EMBER_ERR_PAGE_RANGE);
                 *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
             }
         }
