@@ -72,31 +72,37 @@ gated_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ gat
 }
 
 // ---------------------------------------------------------------------------------- per-group RMS norm with gate
-// One warp per (token, group).  gate_mode 0: none; 1: out *= sigmoid(gate) after the norm; 2: v *= silu(gate) before.
-template <typename TO>
-__global__ void group_norm_gate_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gate, int ldg,
-                                       const float* __restrict__ w, int w_stride, float eps, int gate_mode,
-                                       const float* __restrict__ den4, TO* __restrict__ out, int T, int groups, int V) {
+// TPG threads per (token, group): a warp for the short rows of a head, a whole block of 256 for wide groups (a
+// state-space layer normalises all its channels as one group or a few).  gate_mode 0: none; 1: out *= sigmoid(gate)
+// after the norm; 2: v *= silu(gate) before.
+template <typename TO, int TPG>
+__global__ void __launch_bounds__(256)
+group_norm_gate_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gate, int ldg,
+                       const float* __restrict__ w, int w_stride, float eps, int gate_mode,
+                       const float* __restrict__ den4, TO* __restrict__ out, int T, int groups, int V) {
+    __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= T * groups) return;
-    const int t = warp / groups, g = warp - t * groups;
+    const int row = TPG == 32 ? (blockIdx.x * blockDim.x + threadIdx.x) >> 5 : blockIdx.x;
+    const int lane = TPG == 32 ? (threadIdx.x & 31) : threadIdx.x;
+    if (row >= T * groups) return;
+    const int t = row / groups, g = row - t * groups;
     const float* in = x + (size_t)t * ldx + (size_t)g * V;
     const float* gl = gate ? gate + (size_t)t * ldg + (size_t)g * V : nullptr;
     // den4 (nullable): per (token, group) four floats whose last two are (floor, dot): the group is first divided by
     // max(|dot|, floor) + 1e-6 (the denominator of a matrix memory's read-out)
-    const float inv = den4 ? 1.0f / (fmaxf(fabsf(den4[(size_t)warp * 4 + 3]), den4[(size_t)warp * 4 + 2]) + 1e-6f) : 1.0f;
+    const float inv = den4 ? 1.0f / (fmaxf(fabsf(den4[(size_t)row * 4 + 3]), den4[(size_t)row * 4 + 2]) + 1e-6f) : 1.0f;
     float ss = 0.0f;
-    for (int j = lane; j < V; j += 32) {
+    for (int j = lane; j < V; j += TPG) {
         float v = in[j] * inv;
         if (gate_mode == 2) { const float z = gl[j]; v *= z * sigmoidf_(z); }
         ss = fmaf(v, v, ss);
     }
-    const float r = 1.0f / sqrtf(warp_sum(ss) / (float)V + eps);
+    ss = TPG == 32 ? warp_sum(ss) : block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)V + eps);
     TO* o = out + ((size_t)t * groups + g) * V;
     const float* wg = w + (size_t)g * w_stride;
-    for (int j = lane; j < V; j += 32) {
+    for (int j = lane; j < V; j += TPG) {
         float v = in[j] * inv;
         if (gate_mode == 2) { const float z = gl[j]; v *= z * sigmoidf_(z); }
         v = v * r * wg[j];
@@ -187,15 +193,15 @@ EMBER_API int ember_group_norm_gate(const float* x, int ldx, const float* gate, 
     if (groups <= 0 || V <= 0 || ldx < groups * V) return fail("group_norm_gate: %d groups of %d in rows of %d", groups, V, ldx);
     if (gate_mode < 0 || gate_mode > 2 || (gate_mode && (!gate || ldg < groups * V))) return fail("group_norm_gate: bad gate");
     cudaStream_t st = (cudaStream_t)stream;
-    const long long warps = (long long)T * groups;
-    const unsigned blocks = (unsigned)((warps + 7) / 8);
-    if (out_dtype == EMBER_F32)
-        launch_kernel(group_norm_gate_kernel<float>, blocks, 256, 0, st, x, ldx, gate, ldg, w, w_stride, eps, gate_mode, den4, (float*)out, T, groups, V);
-    else if (out_dtype == EMBER_BF16)
-        launch_kernel(group_norm_gate_kernel<__nv_bfloat16>, blocks, 256, 0, st, x, ldx, gate, ldg, w, w_stride, eps, gate_mode,
-                      den4, (__nv_bfloat16*)out, T, groups, V);
-    else
-        return fail("group_norm_gate: unsupported output dtype %d", out_dtype);
+    const long long rows = (long long)T * groups;
+    const bool wide = V > 512;
+    const unsigned blocks = wide ? (unsigned)rows : (unsigned)((rows + 7) / 8);
+#define EMBER_GNG(TO, TPG) launch_kernel(group_norm_gate_kernel<TO, TPG>, blocks, 256, 0, st, x, ldx, gate, ldg, w, w_stride, eps, \
+                                         gate_mode, den4, (TO*)out, T, groups, V)
+    if (out_dtype == EMBER_F32) { if (wide) EMBER_GNG(float, 256); else EMBER_GNG(float, 32); }
+    else if (out_dtype == EMBER_BF16) { if (wide) EMBER_GNG(__nv_bfloat16, 256); else EMBER_GNG(__nv_bfloat16, 32); }
+    else return fail("group_norm_gate: unsupported output dtype %d", out_dtype);
+#undef EMBER_GNG
     return check_launch("group_norm_gate");
 }
 

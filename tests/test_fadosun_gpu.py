@@ -270,19 +270,19 @@ def test_layer_norm_gate_and_sandwich_kernels(dtype):
         ops.gated_norm_add(y, logits, w, b, 1e-5, True, res, 11, gate_bias=gb)
         want = x.cpu().double() + plain.layer_norm(y.cpu().double() * torch.sigmoid((logits + gb).cpu().double()), w.cpu(), b.cpu(), 1e-5)
         assert _rel(res.cpu(), want) < 1e-6
-    T, groups, V = 9, 3, 44
-    o, gate = torch.randn(T, groups * V + 5, generator=g).to(dev), torch.randn(T, 7 + groups * V, generator=g).to(dev)
-    for per_group, mode in ((True, ops.GATE_SIGMOID_AFTER), (False, ops.GATE_SILU_BEFORE), (False, ops.GATE_NONE)):
-        w = (1 + 0.1 * torch.randn(groups * V if per_group else V, generator=g)).to(dev)
-        out = torch.empty(T, groups * V, device=dev, dtype=dtype)
-        ops.group_norm_gate(o, 5, gate, 7, w, per_group, 1e-6, mode, out, T, groups, V)
-        v, z = o[:, 5:].cpu().double().view(T, groups, V), gate[:, 7:].cpu().double().view(T, groups, V)
-        if mode == ops.GATE_SILU_BEFORE:
-            v = v * plain.silu(z)
-        want = plain.rms_div(v, 1e-6) * (w.cpu().double().view(groups, V) if per_group else w.cpu().double())
-        if mode == ops.GATE_SIGMOID_AFTER:
-            want = want * torch.sigmoid(z)
-        assert _rel(out.float().cpu().view(T, groups, V), want) < (5e-3 if dtype == torch.bfloat16 else 1e-6)
+    for T, groups, V in ((9, 3, 44), (5, 2, 600)):            # a warp per short group, a block per wide one
+        o, gate = torch.randn(T, groups * V + 5, generator=g).to(dev), torch.randn(T, 7 + groups * V, generator=g).to(dev)
+        for per_group, mode in ((True, ops.GATE_SIGMOID_AFTER), (False, ops.GATE_SILU_BEFORE), (False, ops.GATE_NONE)):
+            w = (1 + 0.1 * torch.randn(groups * V if per_group else V, generator=g)).to(dev)
+            out = torch.empty(T, groups * V, device=dev, dtype=dtype)
+            ops.group_norm_gate(o, 5, gate, 7, w, per_group, 1e-6, mode, out, T, groups, V)
+            v, z = o[:, 5:].cpu().double().view(T, groups, V), gate[:, 7:].cpu().double().view(T, groups, V)
+            if mode == ops.GATE_SILU_BEFORE:
+                v = v * plain.silu(z)
+            want = plain.rms_div(v, 1e-6) * (w.cpu().double().view(groups, V) if per_group else w.cpu().double())
+            if mode == ops.GATE_SIGMOID_AFTER:
+                want = want * torch.sigmoid(z)
+            assert _rel(out.float().cpu().view(T, groups, V), want) < (5e-3 if dtype == torch.bfloat16 else 1e-6)
 
 
 # ------------------------------------------------------------------------ through the entry point
