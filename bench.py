@@ -582,7 +582,7 @@ def main() -> int:
                          "(kernels serialised: EMBER_PDL=0 and no CUDA graphs are set by this flag)")
     ap.add_argument("--page-tokens", type=int, default=PAGE_TOKENS, choices=[16, 32, 64], help="tokens per cache page")
     ap.add_argument("--workload", default="default", choices=["default", "serving-8b", "qwen3-32b", "fadosun"],
-                    help="default: the Qwen3-1.7B line the contract asks for; serving-8b and qwen3-32b are BASELINE's fourth "
+                    help="default: the Qwen3-1.7B line; serving-8b and qwen3-32b are BASELINE's fourth "
                          "and fifth configurations; fadosun: that design beside Qwen3 at equal sizes (with --breakdown "
                          "also per kernel); one JSON line each")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
