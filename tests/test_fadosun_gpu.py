@@ -59,11 +59,11 @@ def make_requests(name, lengths, seed):
     return {f"r{i}": rng.integers(0, FADOSUN[name]["json"]["vocab"], size=n).tolist() for i, n in enumerate(lengths)}
 
 
-def replay(model_dir, dtype, steps, capacity, page_tokens=16, max_requests=4, **kw):
+def replay(model_dir, dtype, steps, capacity, page_tokens=16, max_requests=4, max_batch_tokens=512, **kw):
     import tempfile
     from ember_b200.engine.replay import TraceReplayer
     from ember_b200.engine.runner import ModelRunner
-    runner = ModelRunner.from_dir(model_dir, dtype=dtype, capacity_tokens=capacity, max_batch_tokens=512,
+    runner = ModelRunner.from_dir(model_dir, dtype=dtype, capacity_tokens=capacity, max_batch_tokens=max_batch_tokens,
                                   max_requests=max_requests, page_tokens=page_tokens, **kw)
     with tempfile.TemporaryDirectory() as out:
         rp = TraceReplayer(runner, out)
@@ -107,6 +107,16 @@ def test_long_decoding_through_graphs_equals_the_prompt(dtype, dirs, plain_logit
     assert_close(collect(steps, outputs), plain_logits("p", requests), dtype, "long decoding")
     eager, _ = replay(dirs["p"], dtype, steps, 320, cuda_graphs=False)
     assert max(float(np.abs(outputs[k] - eager[k]).max()) for k in outputs) < (1e-5 if dtype == "float32" else 1e-1)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_then_decoding(dtype, dirs, plain_logits):
+    """1,300 tokens at a real model's head sizes: keys more than a thousand positions back and a state that has seen
+    as many tokens, as one prompt with a decoded tail and as portions of 500."""
+    requests = make_requests("r", (1300,), seed=17)
+    for steps in (trace_tail_decode(requests, tail=24), trace_portions(requests, sizes=(500, 37, 500, 2))):
+        outputs, _ = replay(dirs["r"], dtype, steps, 1344, page_tokens=64, max_batch_tokens=2048)
+        assert_close(collect(steps, outputs), plain_logits("r", requests), dtype, "long prompt")
 
 
 def test_a_slot_used_again_starts_from_zero(dirs, plain_logits):
@@ -283,6 +293,28 @@ def test_layer_norm_gate_and_sandwich_kernels(dtype):
             if mode == ops.GATE_SIGMOID_AFTER:
                 want = want * torch.sigmoid(z)
             assert _rel(out.float().cpu().view(T, groups, V), want) < (5e-3 if dtype == torch.bfloat16 else 1e-6)
+
+
+# ------------------------------------------------------------------------ through the programs
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, dirs, plain_logits, tmp_path):
+    """bin/trace_run as a user runs it (config.json without the low-rank sizes, four state slots, steps on standard
+    input): portions beside single tokens of up to four live requests, and a step larger than any one batch."""
+    import subprocess
+    import sys
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    requests = make_requests("q", (300, 41, 75, 2, 33, 64), seed=9)
+    steps = trace_mixed(requests, live=4, seed=1, max_portion=70)
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", dirs["q"], "--dtype", dtype, "--out", str(out),
+         "--max-tokens", str(max_live_tokens(steps))],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    vocab = FADOSUN["q"]["json"]["vocab"]
+    outputs = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab) for s in steps}
+    assert_close(collect(steps, outputs), plain_logits("q", requests), dtype, "trace_run")
 
 
 # ------------------------------------------------------------------------ through the entry point
