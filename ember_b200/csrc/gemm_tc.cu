@@ -220,7 +220,7 @@ using namespace ember;
 EMBER_API int ember_gemm_tc_supported(int M, int N, int K, int epilogue) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 8) return 0;                       // TMA needs 16-byte row pitch
-    if (epilogue == 3 && (N & 1)) return 0;
+    if ((epilogue == 3 || epilogue == 6) && (N & 1)) return 0;       // 6: the gated epilogue with relu
     if (epilogue == 5 && M > 128) return 0;    // the sums stay in the scratch of the small-M product
     return 1;
 }
@@ -237,6 +237,8 @@ EMBER_API long long ember_gemm_tc_scratch_floats(int max_tokens_swapped, int N) 
 EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, int M, int N, int K, int epilogue,
                             float* scratch, long long scratch_floats, int num_sms, int split_mode, int* err, void* stream) {
     if (M <= 0 || N <= 0) return 0;
+    const int act = epilogue == 6 ? 1 : 0;             // epilogue 6: relu(gate) * up, the gated epilogue with another activation
+    if (epilogue == 6) epilogue = 3;
     const bool sums = epilogue == 5;
     if (sums) {
         if (M > 128 || !scratch || scratch_floats < (long long)M * N)
@@ -250,7 +252,7 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
     cudaStream_t st = (cudaStream_t)stream;
 
     GemmTcParams p;
-    p.M = M; p.N = N; p.K = K;
+    p.M = M; p.N = N; p.K = K; p.act = act;
     p.swapped = M <= 128 ? 1 : 0;
     p.num_k_blocks = (K + TILE_K - 1) / TILE_K;
     int row_tiles, col_tiles;
@@ -411,11 +413,11 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
         const bool by4 = n_out % 4 == 0 && ldc % 4 == 0 && p.accum_ld % 4 == 0 && ((((uintptr_t)p.accum) | ((uintptr_t)out)) & 15) == 0;
         if (by4) {
             const unsigned blocks = (unsigned)((total / 4 + 255) / 256);
-            if (epilogue == 3) launch_kernel(gemm_tc_finalize4_kernel<3>, blocks, 256, 0, st, p.accum, p.accum_ld, out, ldc, M, n_out);
-            else if (epilogue == 1) launch_kernel(gemm_tc_finalize4_kernel<1>, blocks, 256, 0, st, p.accum, p.accum_ld, out, ldc, M, n_out);
-            else launch_kernel(gemm_tc_finalize4_kernel<0>, blocks, 256, 0, st, p.accum, p.accum_ld, out, ldc, M, n_out);
+            if (epilogue == 3) launch_kernel(gemm_tc_finalize4_kernel<3>, blocks, 256, 0, st, p.accum, p.accum_ld, out, ldc, M, n_out, act);
+            else if (epilogue == 1) launch_kernel(gemm_tc_finalize4_kernel<1>, blocks, 256, 0, st, p.accum, p.accum_ld, out, ldc, M, n_out, 0);
+            else launch_kernel(gemm_tc_finalize4_kernel<0>, blocks, 256, 0, st, p.accum, p.accum_ld, out, ldc, M, n_out, 0);
         } else {
-            launch_kernel(gemm_tc_finalize_kernel, (unsigned)((total + 255) / 256), 256, 0, st, p.accum, p.accum_ld, out, ldc, M, N, epilogue);
+            launch_kernel(gemm_tc_finalize_kernel, (unsigned)((total + 255) / 256), 256, 0, st, p.accum, p.accum_ld, out, ldc, M, N, epilogue, act);
         }
         return check_launch("gemm_tc_finalize");
     }

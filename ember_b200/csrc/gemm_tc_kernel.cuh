@@ -45,7 +45,8 @@ struct GemmTcParams {
     int stages;
     int num_k_blocks;     // ceil(K / TILE_K)
     int k_blocks_per_split;
-    int epilogue;         // 0 store bf16, 1 store fp32, 2 add fp32, 3 silu(gate)*up -> bf16
+    int epilogue;         // 0 store bf16, 1 store fp32, 2 add fp32, 3 act(gate)*up -> bf16
+    int act;              // epilogue 3: 0 silu, 1 relu
     void* out;
     int ldc;
     float* accum;         // atomic split-K target: fp32 [M, accum_ld] (the residual itself for epilogue 2)
@@ -140,7 +141,9 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+__device__ __forceinline__ float gate_mul(float g, float u, int act) {      // act(gate) * up: act 0 silu, 1 relu
+    return (act ? fmaxf(g, 0.0f) : g / (1.0f + __expf(-g))) * u;
+}
 
 // Fused epilogue of 16 consecutive output columns of one token row (normal orientation):
 // store bf16 / store fp32 / add into the fp32 residual / silu(gate) * up.
@@ -184,10 +187,10 @@ __device__ __forceinline__ void store_chunk_normal(const GemmTcParams& p, int m,
             __nv_bfloat162* h = (__nv_bfloat162*)&q;
 #pragma unroll
             for (int j = 0; j < 4; j++)
-                h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]), silu_mul(v[4 * j + 2], v[4 * j + 3]));
+                h[j] = __floats2bfloat162_rn(gate_mul(v[4 * j], v[4 * j + 1], p.act), gate_mul(v[4 * j + 2], v[4 * j + 3], p.act));
             *(uint4*)dst = q;
         } else {
-            for (int j = 0; j + 1 < nv; j += 2) dst[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+            for (int j = 0; j + 1 < nv; j += 2) dst[j >> 1] = __float2bfloat16_rn(gate_mul(v[j], v[j + 1], p.act));
         }
     }
 }
@@ -634,7 +637,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
                     uint8_t* row = turn + (size_t)c * row_bytes;
                     if (p.epilogue == 3) {
                         const float other = __shfl_xor_sync(0xffffffffu, x, 1);             // gate rows are even, up rows odd
-                        if ((lane & 1) == 0) reinterpret_cast<__nv_bfloat16*>(row)[r >> 1] = __float2bfloat16_rn(silu_mul(x, other));
+                        if ((lane & 1) == 0) reinterpret_cast<__nv_bfloat16*>(row)[r >> 1] = __float2bfloat16_rn(gate_mul(x, other, p.act));
                     } else if (p.epilogue == 0) {
                         reinterpret_cast<__nv_bfloat16*>(row)[r] = __float2bfloat16_rn(x);
                     } else {
@@ -683,7 +686,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
                             const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
                             const int m = m0 + j;
                             if ((lane & 1) == 0 && n + 1 < p.N && m < p.M)
-                                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(silu_mul(v[j], other));
+                                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(gate_mul(v[j], other, p.act));
                         }
                         continue;
                     }
@@ -732,7 +735,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
                     g += recv[((size_t)s * RP + 2 * pr) * C + c];
                     u += recv[((size_t)s * RP + 2 * pr + 1) * C + c];
                 }
-                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(silu_mul(g, u));
+                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(gate_mul(g, u, p.act));
             }
         } else {
             for (int idx = threadIdx.x; idx < rows_here * C; idx += GEMM_THREADS) {
@@ -920,7 +923,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __
 
 // Split-K finalize for the store epilogues: out = epilogue(accum), accum = 0.
 __global__ void gemm_tc_finalize_kernel(float* __restrict__ accum, int accum_ld, void* __restrict__ out, int ldc, int M,
-                                        int N, int epilogue) {
+                                        int N, int epilogue, int act = 0) {
     pdl_launch_dependents();
     pdl_wait();
     const int n_out = epilogue == 3 ? N / 2 : N;
@@ -932,7 +935,7 @@ __global__ void gemm_tc_finalize_kernel(float* __restrict__ accum, int accum_ld,
         const float g = a[2 * j], u = a[2 * j + 1];
         a[2 * j] = 0.0f;
         a[2 * j + 1] = 0.0f;
-        ((__nv_bfloat16*)out)[(size_t)m * ldc + j] = __float2bfloat16_rn(silu_mul(g, u));
+        ((__nv_bfloat16*)out)[(size_t)m * ldc + j] = __float2bfloat16_rn(gate_mul(g, u, act));
     } else {
         const float c = a[j];
         a[j] = 0.0f;
@@ -944,7 +947,8 @@ __global__ void gemm_tc_finalize_kernel(float* __restrict__ accum, int accum_ld,
 // The same, four outputs a thread (16-byte loads of the sums, one 8- or 16-byte store): the row widths are multiples
 // of four and the rows 16-byte aligned.  At 64 tokens the one-element kernel took 11 us a call, a tenth of the step.
 template <int EPI>
-__global__ void gemm_tc_finalize4_kernel(float* __restrict__ accum, int accum_ld, void* __restrict__ out, int ldc, int M, int n_out) {
+__global__ void gemm_tc_finalize4_kernel(float* __restrict__ accum, int accum_ld, void* __restrict__ out, int ldc, int M, int n_out,
+                                         int act = 0) {
     pdl_launch_dependents();
     pdl_wait();
     const int groups = n_out >> 2;
@@ -958,7 +962,7 @@ __global__ void gemm_tc_finalize4_kernel(float* __restrict__ accum, int accum_ld
         const float4 x0 = a[0], x1 = a[1];
         a[0] = zero;
         a[1] = zero;
-        r0 = silu_mul(x0.x, x0.y); r1 = silu_mul(x0.z, x0.w); r2 = silu_mul(x1.x, x1.y); r3 = silu_mul(x1.z, x1.w);
+        r0 = gate_mul(x0.x, x0.y, act); r1 = gate_mul(x0.z, x0.w, act); r2 = gate_mul(x1.x, x1.y, act); r3 = gate_mul(x1.z, x1.w, act);
     } else {
         float4* a = reinterpret_cast<float4*>(accum + (size_t)m * accum_ld + j);
         const float4 x = a[0];

@@ -81,7 +81,7 @@ EMBER_API int ember_gemm_tc_noalloc(const void* A, const void* W, void* out, int
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
 
     GemmTcParams p;
-    p.M = M; p.N = N; p.K = K;
+    p.M = M; p.N = N; p.K = K; p.act = 0;
     p.swapped = 1;
     p.num_k_blocks = (K + TILE_K - 1) / TILE_K;
     p.block_cols = ((M + 15) / 16) * 16;

@@ -17,6 +17,8 @@ from .csrc import build
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SILU_MUL = 0, 1, 2, 3
 EPI_SUMS = 5      # tensor-core product of at most 128 tokens: the fp32 sums stay in the split-K scratch
+EPI_RELU_MUL = 6  # the gated epilogue with relu: relu(c[2j]) * c[2j + 1]
+GATED_EPILOGUES = (EPI_SILU_MUL, EPI_RELU_MUL)
 
 
 class KernelError(RuntimeError):
@@ -217,8 +219,8 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilo
     N, K = w.shape
     if a.shape[-1] != K:
         raise KernelError(f"gemm: activations of width {a.shape[-1]} against weights {tuple(w.shape)}")
-    n_out = N // 2 if epilogue == EPI_SILU_MUL else N
-    want = a.dtype if epilogue in (EPI_STORE, EPI_SILU_MUL) else torch.float32
+    n_out = N // 2 if epilogue in GATED_EPILOGUES else N
+    want = a.dtype if epilogue in (EPI_STORE,) + GATED_EPILOGUES else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm: epilogue {epilogue} writes {want}, the output is {out.dtype}")
     if out.shape[-1] != n_out or out.numel() < M * n_out or a.numel() < M * K:
@@ -356,7 +358,7 @@ def gemm_tc_usable(x: torch.Tensor, w: torch.Tensor, bias, epilogue: int) -> boo
     if not TC_ENABLED or bias is not None or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
     n, k = w.shape
-    return k % 8 == 0 and not (epilogue == EPI_SILU_MUL and n % 2)
+    return k % 8 == 0 and not (epilogue in GATED_EPILOGUES and n % 2)
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogue: int = EPI_STORE,
@@ -382,8 +384,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogu
               c_void_p(stream if stream is not None else current_stream_ptr()))
         return scratch[:M * N].view(M, N)
     _check(out, "out")
-    n_out = N // 2 if epilogue == EPI_SILU_MUL else N
-    want = torch.bfloat16 if epilogue in (EPI_STORE, EPI_SILU_MUL) else torch.float32
+    n_out = N // 2 if epilogue in GATED_EPILOGUES else N
+    want = torch.bfloat16 if epilogue in (EPI_STORE,) + GATED_EPILOGUES else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm: epilogue {epilogue} writes {want}, the output is {out.dtype}")
     if out.shape[-1] != n_out or out.numel() < M * n_out or a.numel() < M * K:

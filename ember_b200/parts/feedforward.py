@@ -50,13 +50,7 @@ class GatedMLP(FeedForward):
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
         s = self.spec
         act = ctx.buf("gated_mlp.act", (ctx.max_tokens, s.intermediate_size), self.rt.dtype)
-        if s.activation == "silu":
-            self.gate_up(ctx, x, act, ctx.T, ops.EPI_SILU_MUL)
-        else:
-            # other activations: the product stores its interleaved (gate, up) pairs and a kernel of its own folds them
-            both = ctx.buf("gated_mlp.gate_up", (ctx.max_tokens, 2 * s.intermediate_size), self.rt.dtype)
-            self.gate_up(ctx, x, both, ctx.T, ops.EPI_STORE)
-            ops.act_mul_interleaved(both, act, s.activation, ctx.T * s.intermediate_size, stream=ctx.stream)
+        self.gate_up(ctx, x, act, ctx.T, ops.EPI_SILU_MUL if s.activation == "silu" else ops.EPI_RELU_MUL)
         self.down(ctx, act, residual, ctx.T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
 
 

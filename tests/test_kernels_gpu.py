@@ -18,6 +18,8 @@ def ref_epilogue(c, epilogue, prev=None):
     if epilogue == 3:
         g, u = c[:, 0::2], c[:, 1::2]
         return g / (1 + torch.exp(-g)) * u
+    if epilogue == 6:                                   # the gated epilogue with relu
+        return torch.relu(c[:, 0::2]) * c[:, 1::2]
     if epilogue == 2:
         return prev + c
     return c
@@ -28,7 +30,7 @@ def ref_epilogue(c, epilogue, prev=None):
                                    (8, 4096, 2048), (5, 2048, 6144), (16, 12288, 1024), (100, 640, 4096),
                                    (2048, 4096, 512), (777, 1500, 320), (4200, 2300, 136), (130, 100, 64),
                                    (512, 2048, 6144), (260, 204, 1544)])      # few tiles, long K: the adding epilogue cuts K
-@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3, 6])
 @pytest.mark.parametrize("split_mode", [0, 1, 2, 3, 4, 5])
 def test_gemm_tc(M, N, K, epilogue, split_mode):
     """split_mode: 0 as the engine chooses, 1 atomics, 2 cluster sums, 3 one tile per block, 4 pairs of SMs
@@ -37,7 +39,7 @@ def test_gemm_tc(M, N, K, epilogue, split_mode):
     torch.manual_seed(M * 7 + N + K + epilogue)
     a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
-    n_out = N // 2 if epilogue == 3 else N
+    n_out = N // 2 if epilogue in (3, 6) else N
     prev = torch.randn(M, n_out, device="cuda")
     out = prev.clone() if epilogue in (1, 2) else torch.zeros(M, n_out, device="cuda", dtype=torch.bfloat16)
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -45,7 +47,7 @@ def test_gemm_tc(M, N, K, epilogue, split_mode):
     ops.gemm_tc(a, w, out, M, epilogue, err=err, split_mode=split_mode)
     want = ref_epilogue(a.float() @ w.float().t(), epilogue, prev)
     assert int(err.item()) == 0
-    tol = 5e-3 if epilogue in (0, 3) else 1e-5          # bf16 rounding of the output, else fp32 accumulation only
+    tol = 5e-3 if epilogue in (0, 3, 6) else 1e-5       # bf16 rounding of the output, else fp32 accumulation only
     assert rel(out.float(), want) < tol
     if M <= 128:                                        # the split-K scratch is left zeroed
         assert float(ops._tc_scratch[a.device].abs().max()) == 0.0
@@ -53,7 +55,7 @@ def test_gemm_tc(M, N, K, epilogue, split_mode):
 
 @pytest.mark.parametrize("M,N,K", [(17, 2048, 264), (64, 2048, 2048), (128, 24576, 128), (100, 640, 264), (33, 1000, 72),
                                    (128, 1160, 136), (70, 20000, 64)])
-@pytest.mark.parametrize("epilogue", [0, 1, 3])
+@pytest.mark.parametrize("epilogue", [0, 1, 3, 6])
 def test_gemm_tc_whole_k_more_than_16_tokens(M, N, K, epilogue):
     """17 to 128 tokens with K in one part (forced with split_mode 17, and what the planner picks for a matrix of
     more tiles than SMs): the block turns its tile in shared memory and stores whole pieces of token rows.  1,000
@@ -63,14 +65,14 @@ def test_gemm_tc_whole_k_more_than_16_tokens(M, N, K, epilogue):
     torch.manual_seed(M + N + K + epilogue)
     a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
-    n_out = N // 2 if epilogue == 3 else N
+    n_out = N // 2 if epilogue in (3, 6) else N
     want = ref_epilogue(a.float() @ w.float().t(), epilogue)
     for mode in (17, 0):
         out = torch.full((M + 1, n_out), 7.0, device="cuda", dtype=torch.float32 if epilogue == 1 else torch.bfloat16)
         err = torch.zeros(1, dtype=torch.int32, device="cuda")
         ops.gemm_tc(a, w, out, M, epilogue, err=err, split_mode=mode)
         assert int(err.item()) == 0
-        assert rel(out[:M].float(), want) < (5e-3 if epilogue in (0, 3) else 1e-5)
+        assert rel(out[:M].float(), want) < (5e-3 if epilogue in (0, 3, 6) else 1e-5)
         assert float((out[M].float() - 7.0).abs().max()) == 0.0          # the row after the step's tokens is not touched
 
 
@@ -85,18 +87,18 @@ def test_gemm_tc_tile_widths(cols, split_mode, monkeypatch):
     a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    for epilogue in (0, 2, 3):
-        n_out = N // 2 if epilogue == 3 else N
+    for epilogue in (0, 2, 3, 6):
+        n_out = N // 2 if epilogue in (3, 6) else N
         prev = torch.randn(M, n_out, device="cuda")
         out = prev.clone() if epilogue == 2 else torch.zeros(M, n_out, device="cuda", dtype=torch.bfloat16)
         ops.gemm_tc(a, w, out, M, epilogue, err=err, split_mode=split_mode)
         want = ref_epilogue(a.float() @ w.float().t(), epilogue, prev)
         assert int(err.item()) == 0
-        assert rel(out.float(), want) < (5e-3 if epilogue in (0, 3) else 1e-5)
+        assert rel(out.float(), want) < (5e-3 if epilogue in (0, 3, 6) else 1e-5)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 50, 7), (5, 1000, 96), (70, 130, 33), (200, 192, 64)])
-@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3, 6])
 @pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                      (torch.bfloat16, torch.float32)])
 def test_gemm_simt(M, N, K, epilogue, adt, wdt):
@@ -105,13 +107,13 @@ def test_gemm_simt(M, N, K, epilogue, adt, wdt):
     a = (torch.randn(M, K, device="cuda") * 0.5).to(adt)
     w = (torch.randn(N, K, device="cuda") * 0.5).to(wdt)
     bias = torch.randn(N, device="cuda")
-    n_out = N // 2 if epilogue == 3 else N
+    n_out = N // 2 if epilogue in (3, 6) else N
     prev = torch.randn(M, n_out, device="cuda")
     out = prev.clone() if epilogue in (1, 2) else torch.zeros(M, n_out, device="cuda", dtype=adt)
     ops.gemm_simt(a, w, out, M, epilogue, bias=bias)
     c = (a.double() @ w.double().t() + bias.double()).float()
     want = ref_epilogue(c, epilogue, prev)
-    tol = 5e-3 if (adt == torch.bfloat16 and epilogue in (0, 3)) else 2e-6
+    tol = 5e-3 if (adt == torch.bfloat16 and epilogue in (0, 3, 6)) else 2e-6
     assert rel(out.float(), want) < tol
 
 
