@@ -4,7 +4,6 @@
 //   group_norm_gate   a token's row cut into groups, each divided by its own root mean square, times a weight,
 //                     with a gate before (silu) or after (sigmoid) the norm
 //   scaled_sum        out (+)= a x + b y
-//   act_mul           out[m, j] = act(x[m, 2j]) * x[m, 2j + 1] for an unfused gate/up product
 // Rows are read from the fp32 residual stream or from fp32 results of a product; a row is reduced by one block
 // (or one warp for the short rows of a head) in an order fixed by the thread layout.
 #include "common.cuh"
@@ -121,38 +120,6 @@ __global__ void scaled_sum_kernel(const float* __restrict__ x, float a, const fl
     out[i] = accumulate ? out[i] + v : v;
 }
 
-// act 0: silu, 1: relu.  bf16 rows in whole 16-byte pieces: 8 (gate, up) pairs in (two loads), 8 results out.
-__global__ void act_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int act, size_t n8) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n8) return;
-    const uint4 a = reinterpret_cast<const uint4*>(x)[2 * i], b = reinterpret_cast<const uint4*>(x)[2 * i + 1];
-    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
-    float r[8];
-#pragma unroll
-    for (int k = 0; k < 8; k++) {
-        const float2 gu = __bfloat1622float2(k < 4 ? pa[k] : pb[k - 4]);
-        r[k] = (act == 1 ? fmaxf(gu.x, 0.0f) : gu.x / (1.0f + expf(-gu.x))) * gu.y;
-    }
-    uint4 o;
-    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-    for (int k = 0; k < 4; k++) po[k] = __floats2bfloat162_rn(r[2 * k], r[2 * k + 1]);
-    reinterpret_cast<uint4*>(out)[i] = o;
-}
-
-template <typename T>
-__global__ void act_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int act, size_t n_out) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_out) return;
-    const float g = to_float(x[2 * i]), u = to_float(x[2 * i + 1]);
-    out[i] = from_float<T>((act == 1 ? fmaxf(g, 0.0f) : g / (1.0f + expf(-g))) * u);
-}
-
 }  // namespace ember
 
 using namespace ember;
@@ -209,21 +176,4 @@ EMBER_API int ember_scaled_sum(const float* x, float a, const float* y, float b,
     if (n <= 0) return 0;
     launch_kernel(scaled_sum_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, x, a, y, b, out, accumulate, (size_t)n);
     return check_launch("scaled_sum");
-}
-
-EMBER_API int ember_act_mul_interleaved(const void* x, void* out, int dtype, int act, long long n_out, void* stream) {
-    if (n_out <= 0) return 0;
-    if (act != 0 && act != 1) return fail("act_mul: unknown activation %d", act);
-    cudaStream_t st = (cudaStream_t)stream;
-    const unsigned blocks = (unsigned)((n_out + 255) / 256);
-    if (dtype == EMBER_F32)
-        launch_kernel(act_mul_kernel<float>, blocks, 256, 0, st, (const float*)x, (float*)out, act, (size_t)n_out);
-    else if (dtype == EMBER_BF16 && n_out % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0)
-        launch_kernel(act_mul_bf16x8_kernel, (unsigned)((n_out / 8 + 255) / 256), 256, 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, act,
-                      (size_t)(n_out / 8));
-    else if (dtype == EMBER_BF16)
-        launch_kernel(act_mul_kernel<__nv_bfloat16>, blocks, 256, 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, act, (size_t)n_out);
-    else
-        return fail("act_mul: unsupported dtype %d", dtype);
-    return check_launch("act_mul");
 }

@@ -645,18 +645,7 @@ def scaled_sum(x: torch.Tensor, a: float, y: Optional[torch.Tensor], b: float, o
           _stream(stream))
 
 
-ACTIVATIONS = {"silu": 0, "relu": 1}
-
-
-def act_mul_interleaved(x: torch.Tensor, out: torch.Tensor, activation: str, n_out: int, stream: Optional[int] = None) -> None:
-    """out[m, j] = act(x[m, 2j]) * x[m, 2j + 1] for an unfused gate/up product over interleaved rows."""
-    _check(x, "x")
-    _check(out, "out", x.dtype)
-    if activation not in ACTIVATIONS or x.numel() < 2 * n_out or out.numel() < n_out:
-        raise KernelError(f"act_mul: activation {activation!r}, {n_out} outputs")
-    lib = _lib("norm_gate")
-    _call(lib, lib.ember_act_mul_interleaved, _p(x), _p(out), c_int(dtype_code(x.dtype)), c_int(ACTIVATIONS[activation]),
-          c_longlong(n_out), _stream(stream))
+ACTIVATIONS = ("silu", "relu")      # what the gated epilogue of the products takes (EPI_SILU_MUL, EPI_RELU_MUL)
 
 
 # -------------------------------------------------------------------- recurrent mixers (csrc/recurrent.cu)
