@@ -172,6 +172,9 @@ class CacheManager:
         self.core = self._lib.ember_cache_create(G, arr(kinds), arr(windows), arr(pages), int(page_tokens), int(max_requests))
         if not self.core:
             raise CacheError("the cache core could not be created")
+        for gi, (need, _) in enumerate(grouped):
+            if need.kind == "window" and getattr(need, "keep_first", 0) > 0:
+                self._lib.ember_cache_set_keep(self.core, gi, int(need.keep_first))
         self.groups: List[CacheGroup] = []
         for gi, (need, layers) in enumerate(grouped):
             pool = None

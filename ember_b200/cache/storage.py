@@ -30,8 +30,8 @@ def cache_bytes_per_token(needs, dtype: torch.dtype) -> int:
     same number of tokens): keys and values of every layer of the group.  ``needs`` is what
     ``CausalLM.cache_needs`` returns."""
     elem = torch.empty(0, dtype=dtype).element_size()
-    return sum(n.num_kv_heads * (n.head_dim + (n.value_dim or n.head_dim)) * elem for n in needs.values()
-               if n is not None and n.kind in ("full", "window"))
+    return sum(n.num_kv_heads * (n.head_dim + (0 if n.keys_only else (n.value_dim or n.head_dim))) * elem
+               for n in needs.values() if n is not None and n.kind in ("full", "window"))
 
 
 def state_bytes_per_request(needs) -> int:
@@ -56,6 +56,11 @@ class CacheStorage:
         for g in manager.groups:
             if g.paged:
                 n = g.need
+                if n.keys_only:
+                    # one row per token and head serves as key and value: [layers, pages, kv_heads, page_tokens, size]
+                    self._paged[g.index] = (torch.zeros((len(g.layers), max(1, g.pool.n_pages), n.num_kv_heads, g.page_tokens,
+                                                         n.head_dim), dtype=dtype, device=device),)
+                    continue
                 if n.value_dim and n.value_dim != n.head_dim:
                     # values of another size than keys: two tensors [layers, pages, kv_heads, page_tokens, size]
                     self._paged[g.index] = tuple(
@@ -80,7 +85,7 @@ class CacheStorage:
         if g.paged:
             t = self._paged[gi]
             if isinstance(t, tuple):
-                return LayerCache(group=gi, page_tokens=g.page_tokens, k=t[0][li], v=t[1][li])
+                return LayerCache(group=gi, page_tokens=g.page_tokens, k=t[0][li], v=t[1][li] if len(t) > 1 else None)
             return LayerCache(group=gi, page_tokens=g.page_tokens, k=t[li, 0], v=t[li, 1])
         return LayerCache(group=gi, page_tokens=g.page_tokens, state=self._state[gi][li])
 

@@ -1,16 +1,19 @@
 """Typed configurations and the architecture registry."""
-from .spec import (AttentionSpec, ConfigError, GatedDeltaSpec, GatedMLPSpec, LayerNormSpec, LayerSpec, MatrixMemorySpec,
-                   ModelSpec, NoPositionSpec, ParallelMixerSpec, PartSpec, RMSNormSpec, RotarySpec, ScheduleEntry,
-                   SigmoidAttentionSpec, SigmoidGateSpec, StateSpaceSpec, default_schedule)
+from .spec import (AttentionSpec, ConfigError, GatedDeltaSpec, GatedLinearAttentionSpec, GatedMLPSpec, LatentAttentionSpec,
+                   LayerNormSpec, LayerSpec, MatrixMemorySpec, ModelSpec, NoPositionSpec, ParallelMixerSpec, PartSpec,
+                   RMSNormSpec, RotarySpec, RoutedMLPSpec, ScheduleEntry, SigmoidAttentionSpec, SigmoidGateSpec,
+                   SinkAttentionSpec, StateSpaceSpec, default_schedule)
 from .registry import (config_from_dict, load_config, load_model_spec, register_architecture,
                        registered_architectures, resolve_architecture)
 from .qwen3 import Qwen3Config
 from .fadosun import FadosunConfig
+from .zufusun import ZufusunConfig
 
 __all__ = [
     "AttentionSpec", "ConfigError", "GatedMLPSpec", "LayerSpec", "ModelSpec", "NoPositionSpec", "PartSpec",
     "RMSNormSpec", "RotarySpec", "ScheduleEntry", "default_schedule", "config_from_dict", "load_config",
     "load_model_spec", "register_architecture", "registered_architectures", "resolve_architecture",
     "Qwen3Config", "FadosunConfig", "GatedDeltaSpec", "LayerNormSpec", "MatrixMemorySpec", "ParallelMixerSpec",
-    "SigmoidAttentionSpec", "SigmoidGateSpec", "StateSpaceSpec",
+    "SigmoidAttentionSpec", "SigmoidGateSpec", "StateSpaceSpec", "ZufusunConfig", "GatedLinearAttentionSpec",
+    "LatentAttentionSpec", "RoutedMLPSpec", "SinkAttentionSpec",
 ]

@@ -30,11 +30,13 @@ class PartSpec:
 # ----------------------------------------------------------------------------- norms
 @dataclass(frozen=True)
 class RMSNormSpec(PartSpec):
-    """out = weight * (x * rsqrt(mean(x^2) + eps)); plain weight (not 1 + weight)."""
+    """out = weight * (x * rsqrt(mean(x^2) + eps)); plain weight (not 1 + weight).  The tensor is named prefix +
+    ``weight_suffix``."""
 
     kind: ClassVar[str] = "rmsnorm"
     size: int = 0
     eps: float = 1e-6
+    weight_suffix: str = "weight"
 
 
 @dataclass(frozen=True)
@@ -52,7 +54,9 @@ class LayerNormSpec(PartSpec):
 # ---------------------------------------------------------------- position encodings
 @dataclass(frozen=True)
 class RotarySpec(PartSpec):
-    """Rotate-half rotary embedding over the first ``rotary_dim`` elements of a head."""
+    """Rotary embedding over the first ``rotary_dim`` elements of a head.  ``layout`` "half" pairs element i with
+    i + rotary_dim / 2, "interleaved" pairs element 2i with 2i + 1; the angle of pair i is position * theta^(-2i / rotary_dim)
+    either way."""
 
     kind: ClassVar[str] = "rope"
     head_dim: int = 0
@@ -61,6 +65,7 @@ class RotarySpec(PartSpec):
     # "float32": 1 / powf(theta, 2i / rotary_dim) as the Qwen3 reference computes it; "float64": theta^(-2i / rotary_dim)
     # in double precision, rounded once
     frequency_precision: str = "float32"
+    layout: str = "half"
 
 
 @dataclass(frozen=True)
@@ -112,6 +117,70 @@ class SigmoidAttentionSpec(PartSpec):
     value_dim: int = 0
     scale: float = 1.0
     position: PartSpec = field(default_factory=NoPositionSpec)
+
+
+@dataclass(frozen=True)
+class SinkAttentionSpec(PartSpec):
+    """Grouped-query softmax attention over a paged cache whose denominator also holds exp(sink[head]) (a learned
+    number per head without key or value, tensor ``sink``).  Keys and values may differ in size.  ``qk_norm`` "whole":
+    one RMS norm over the whole query projection and one over the whole key projection (tensors ``q.norm``, ``k.norm``
+    of that size), "none": no norm.  ``window`` > 0: position i sees j <= i with i - j < window or j < keep_first.
+    ``bias``: q, k and v have biases (``q.b`` ...).  Tensors: q, k, v, o."""
+
+    kind: ClassVar[str] = "sink_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    scale: float = 1.0
+    bias: bool = False
+    qk_norm: str = "none"
+    qk_norm_eps: float = 1e-6
+    window: int = 0
+    keep_first: int = 0
+    sink: bool = True
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(PartSpec):
+    """Causal attention whose keys and values are up-projections of a low-rank latent.  Queries: c_q = RMSNorm(W_dq h),
+    q = W_uq c_q, per head [head_dim unrotated | rot_dim rotated].  W_dkv h = [kv_rank | rot_dim]: the first part,
+    RMS-normed, is the latent c; the rest, rotated, is a key part all heads share.  Per head the unrotated key is
+    W_uk c and the value W_uv c; only [c | rotated part] is cached.  A sink per head joins the softmax's denominator,
+    and the concatenated heads are multiplied by sigmoid(W_g h) before W_o.  ``own_kv`` False: the layer has no W_dkv
+    and reads the cache of another layer (the schedule says whose)."""
+
+    kind: ClassVar[str] = "latent_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0             # unrotated query/key elements per head
+    rot_dim: int = 0              # rotated query/key elements per head (the key's are shared by the heads)
+    value_dim: int = 0
+    q_rank: int = 0
+    kv_rank: int = 0
+    scale: float = 1.0
+    norm_eps: float = 1e-6
+    sink: bool = True
+    gate: bool = True
+    own_kv: bool = True
+    position: PartSpec = field(default_factory=NoPositionSpec)
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec(PartSpec):
+    """Linear attention with a decay per head and key channel: S <- diag(alpha) S + k v^T, o = S^T q with
+    alpha = sigmoid(W_a2 W_a1 h + b)^(1 / tau) and q times head_dim^-1/2; per-head RMS norm with a weight shared by
+    the heads, a silu gate, W_o.  ``decay_rank`` 0: read from the stored tensors' shapes."""
+
+    kind: ClassVar[str] = "gla"
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    tau: float = 16.0
+    decay_rank: int = 0
+    norm_eps: float = 1e-6
 
 
 @dataclass(frozen=True)
@@ -204,6 +273,21 @@ class GatedMLPSpec(PartSpec):
     intermediate_size: int = 0
     activation: str = "silu"
     names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec(PartSpec):
+    """Mixture of ``experts`` gated feed-forwards (tensors e0.., each gate, up, down, no biases) of which a token uses
+    the ``top`` with the largest router logits (tensor ``router``, fp32), weighted by the softmax over those logits
+    alone.  An expert: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), W_down (g sigmoid(alpha g) (u + 1))."""
+
+    kind: ClassVar[str] = "routed_mlp"
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    experts: int = 0
+    top: int = 0
+    limit: float = 7.0
+    alpha: float = 1.702
 
 
 # ---------------------------------------------------------------------------- layers

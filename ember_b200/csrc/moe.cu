@@ -1,0 +1,255 @@
+// Routed feed-forward (mixture of experts) over a step's tokens.
+//
+//   route:    per token the `top` largest router logits (ties: the lower index), weights = softmax over those alone;
+//   group:    the (token, choice) pairs ordered by expert: per-expert counts and offsets, the pair behind every
+//             slot, the slot of every pair, and the list of (expert, first slot) row tiles the products walk;
+//   gate_up:  act[slot] = f(W_gu[e] x[token]) for the slots of expert e, the rows of gate and up interleaved so that a
+//             thread holds a (gate, up) pair: g = min(gate, limit), u = clamp(up, -limit, limit),
+//             f = g sigmoid(alpha g) (u + 1);
+//   down:     y[slot] = W_down[e] act[slot]  (fp32);
+//   combine:  out[token] = sum over its choices, in order, of weight * y[slot]  (stored, or added to what is there).
+//
+// Nothing is read back by the host: the products' grids are sized for the most row tiles the step can have and blocks
+// beyond the tile list leave at once, so a decode step can be captured into a CUDA graph.  Every output row is a sum
+// over k in ascending order and independent of its neighbours in the tile, so a token's result depends neither on
+// the other tokens of the step nor on where the grouping put it.
+#include "common.cuh"
+
+EMBER_DEFINE_LAST_ERROR
+
+namespace ember {
+
+constexpr int MOE_MAX_EXPERTS = 256;
+constexpr int MOE_BM = 32, MOE_BN = 64, MOE_BK = 16;
+
+// One warp a token.  A lane holds experts lane, lane + 32, ...
+__global__ void moe_route_kernel(const float* __restrict__ logits, int E, int top, int* __restrict__ sel,
+                                 float* __restrict__ wgt, int T) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (t >= T) return;
+    float z[MOE_MAX_EXPERTS / 32];
+#pragma unroll
+    for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+        const int e = lane + 32 * i;
+        z[i] = e < E ? logits[(size_t)t * E + e] : -INFINITY;
+    }
+    float first = 0.0f, sum = 0.0f, mine = 0.0f;            // lane k keeps the k-th choice's weight (top <= 32)
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+            const int e = lane + 32 * i;
+            if (e < E && z[i] != -INFINITY && (z[i] > best || (z[i] == best && e < at))) { best = z[i]; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+        }
+        if (at == 0x7fffffff) { at = 0; best = first; }     // (no finite logit left: only with NaNs in the row)
+        if (k == 0) first = best;
+        const float w = expf(best - first);
+        sum += w;
+        if (lane == k) mine = w;
+        if (lane == 0) sel[(size_t)t * top + k] = at;
+        if (lane == (at & 31)) {
+#pragma unroll
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++)
+                if (i == (at >> 5)) z[i] = -INFINITY;
+        }
+    }
+    if (lane < top) wgt[(size_t)t * top + lane] = mine / sum;
+}
+
+// One block.  counts / offsets by expert, slots by atomic cursors, then the row tiles.
+// meta: [0] number of row tiles; offsets[E + 1]; tile_expert[max_tiles]; tile_row0[max_tiles].
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ sel, int n_pairs, int E, int* __restrict__ offsets,
+                                                         int* __restrict__ pair_of_slot, int* __restrict__ slot_of_pair,
+                                                         int* __restrict__ n_tiles, int* __restrict__ tile_expert,
+                                                         int* __restrict__ tile_row0, int max_tiles) {
+    __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS + 1], cursor[MOE_MAX_EXPERTS], tstart[MOE_MAX_EXPERTS + 1];
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&count[sel[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tt = 0;
+        for (int e = 0; e < E; e++) {
+            start[e] = at; tstart[e] = tt;
+            at += count[e];
+            tt += (count[e] + MOE_BM - 1) / MOE_BM;
+        }
+        start[E] = at; tstart[E] = tt;
+        *n_tiles = tt < max_tiles ? tt : max_tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+        offsets[e] = start[e];
+        if (e < E) cursor[e] = start[e];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int slot = atomicAdd(&cursor[sel[i]], 1);
+        pair_of_slot[slot] = i;
+        slot_of_pair[i] = slot;
+    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int n = tstart[e + 1] - tstart[e];
+        for (int j = 0; j < n; j++)
+            if (tstart[e] + j < max_tiles) {
+                tile_expert[tstart[e] + j] = e;
+                tile_row0[tstart[e] + j] = start[e] + j * MOE_BM;
+            }
+    }
+}
+
+struct MoeGemmArgs {
+    const void* x; int ld_x;             // rows of the A operand: tokens (gathered through the pairs) or slots
+    const void* w; long long w_expert;   // [E][N][K]
+    void* out; int ld_o;
+    const int* offsets; const int* pair_of_slot; const int* n_tiles; const int* tile_expert; const int* tile_row0;
+    int top;                             // > 0: row of x = pair / top (a token); 0: row of x = slot
+    int N, K;
+    float limit, alpha;
+};
+
+// GATED: N counts interleaved (gate, up) rows, the output has N / 2 columns.
+template <typename TX, typename TW, typename TO, bool GATED>
+__global__ void __launch_bounds__(256) moe_gemm_kernel(MoeGemmArgs p) {
+    __shared__ float As[MOE_BK][MOE_BM + 1];
+    __shared__ float Bs[MOE_BK][MOE_BN + 1];
+    __shared__ int src[MOE_BM];
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)blockIdx.x >= *p.n_tiles) return;
+    const int e = p.tile_expert[blockIdx.x], row0 = p.tile_row0[blockIdx.x], n0 = blockIdx.y * MOE_BN;
+    const int rows = min(MOE_BM, p.offsets[e + 1] - row0);
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    if (threadIdx.x < MOE_BM) {
+        int r = -1;
+        if ((int)threadIdx.x < rows) r = p.top > 0 ? p.pair_of_slot[row0 + threadIdx.x] / p.top : row0 + threadIdx.x;
+        src[threadIdx.x] = r;
+    }
+    __syncthreads();
+    const TW* w = (const TW*)p.w + (size_t)e * p.w_expert;
+    const TX* x = (const TX*)p.x;
+    float acc[2][4] = {};
+    for (int k0 = 0; k0 < p.K; k0 += MOE_BK) {
+        for (int idx = threadIdx.x; idx < MOE_BM * MOE_BK; idx += 256) {
+            const int r = idx / MOE_BK, k = idx - r * MOE_BK;
+            As[k][r] = (src[r] >= 0 && k0 + k < p.K) ? to_float(x[(size_t)src[r] * p.ld_x + k0 + k]) : 0.0f;
+        }
+        for (int idx = threadIdx.x; idx < MOE_BN * MOE_BK; idx += 256) {
+            const int r = idx / MOE_BK, k = idx - r * MOE_BK;
+            const int n = n0 + r;
+            Bs[k][r] = (n < p.N && k0 + k < p.K) ? to_float(w[(size_t)n * p.K + k0 + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < MOE_BK; k++) {
+            float a[2], b[4];
+#pragma unroll
+            for (int i = 0; i < 2; i++) a[i] = As[k][ty * 2 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = Bs[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int r = ty * 2 + i;
+        if (r >= rows) continue;
+        TO* o = (TO*)p.out + (size_t)(row0 + r) * p.ld_o;
+        if (GATED) {
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int n = n0 + tx * 4 + j;
+                if (n >= p.N) continue;
+                const float g = fminf(acc[i][j], p.limit);
+                const float u = fminf(fmaxf(acc[i][j + 1], -p.limit), p.limit);
+                o[n >> 1] = from_float<TO>(g / (1.0f + expf(-p.alpha * g)) * (u + 1.0f));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int n = n0 + tx * 4 + j;
+                if (n < p.N) o[n] = from_float<TO>(acc[i][j]);
+            }
+        }
+    }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wgt, const int* __restrict__ slot_of_pair,
+                                   int top, float* __restrict__ out, int accumulate, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float s = 0.0f;
+        for (int k = 0; k < top; k++)
+            s = fmaf(wgt[(size_t)t * top + k], y[(size_t)slot_of_pair[(size_t)t * top + k] * hidden + i], s);
+        out[(size_t)t * hidden + i] = accumulate ? out[(size_t)t * hidden + i] + s : s;
+    }
+}
+
+}  // namespace ember
+
+using namespace ember;
+
+EMBER_API int ember_moe_tile_rows() { return MOE_BM; }
+
+EMBER_API int ember_moe_route(const float* logits, int T, int E, int top, int* sel, float* wgt, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || top > 32)
+        return fail("moe_route: top %d of %d experts (at most 32 of %d)", top, E, MOE_MAX_EXPERTS);
+    launch_kernel(moe_route_kernel, (unsigned)((T + 7) / 8), 256, 0, (cudaStream_t)stream, logits, E, top, sel, wgt, T);
+    return check_launch("moe_route");
+}
+
+EMBER_API int ember_moe_group(const int* sel, int n_pairs, int E, int* offsets, int* pair_of_slot, int* slot_of_pair, int* n_tiles,
+                              int* tile_expert, int* tile_row0, int max_tiles, void* stream) {
+    if (n_pairs <= 0) return 0;
+    if (E <= 0 || E > MOE_MAX_EXPERTS || max_tiles < n_pairs / MOE_BM + E) return fail("moe_group: %d experts, room for %d tiles", E, max_tiles);
+    launch_kernel(moe_group_kernel, 1, 1024, 0, (cudaStream_t)stream, sel, n_pairs, E, offsets, pair_of_slot, slot_of_pair, n_tiles,
+                  tile_expert, tile_row0, max_tiles);
+    return check_launch("moe_group");
+}
+
+EMBER_API int ember_moe_gemm(const void* x, int x_dtype, int ld_x, const void* w, int w_dtype, long long w_expert, void* out,
+                             int out_dtype, int ld_o, const int* offsets, const int* pair_of_slot, const int* n_tiles,
+                             const int* tile_expert, const int* tile_row0, int max_tiles, int top, int N, int K, int gated,
+                             float limit, float alpha, void* stream) {
+    if (max_tiles <= 0) return 0;
+    if (N <= 0 || K <= 0 || (gated && (N & 1))) return fail("moe_gemm: N=%d K=%d", N, K);
+    MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha};
+    dim3 grid(max_tiles, (N + MOE_BN - 1) / MOE_BN);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int key = x_dtype * 100 + w_dtype * 10 + out_dtype;       // F32 = 0, BF16 = 1
+    if (gated) {
+        if (key == 0) launch_kernel(moe_gemm_kernel<float, float, float, true>, grid, 256, 0, st, p);
+        else if (key == 111) launch_kernel(moe_gemm_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, true>, grid, 256, 0, st, p);
+        else return fail("moe_gemm: unsupported dtypes %d", key);
+    } else {
+        if (key == 0) launch_kernel(moe_gemm_kernel<float, float, float, false>, grid, 256, 0, st, p);
+        else if (key == 110) launch_kernel(moe_gemm_kernel<__nv_bfloat16, __nv_bfloat16, float, false>, grid, 256, 0, st, p);
+        else return fail("moe_gemm: unsupported dtypes %d", key);
+    }
+    return check_launch("moe_gemm");
+}
+
+EMBER_API int ember_moe_combine(const float* y, const float* wgt, const int* slot_of_pair, int T, int top, float* out, int accumulate,
+                                int hidden, void* stream) {
+    if (T <= 0) return 0;
+    launch_kernel(moe_combine_kernel, T, 256, 0, (cudaStream_t)stream, y, wgt, slot_of_pair, top, out, accumulate, hidden);
+    return check_launch("moe_combine");
+}

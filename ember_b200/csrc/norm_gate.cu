@@ -1,8 +1,10 @@
 // Norms and gates around a sublayer, all statistics in fp32:
 //   layer_norm        out[r] = (x - mean) / sqrt(var + eps) * w + b      (var = mean of squared deviations)
-//   gated_norm_add    residual[r] += norm(y[r] * sigmoid(gate_logits[r])) for a layer norm or an RMS norm
+//   gated_norm_add    residual[r] += norm(y[r] * sigmoid(gate_logits[r])) for a layer norm or an RMS norm; the new
+//                     residual row can also be left rounded to bfloat16 (for a sublayer that reads the stream itself)
+//   round_rows        out = bfloat16(x)
 //   group_norm_gate   a token's row cut into groups, each divided by its own root mean square, times a weight,
-//                     with a gate before (silu) or after (sigmoid) the norm
+//                     with a gate before (silu) or after (sigmoid or silu) the norm
 //   scaled_sum        out (+)= a x + b y
 // Rows are read from the fp32 residual stream or from fp32 results of a product; a row is reduced by one block
 // (or one warp for the short rows of a head) in an order fixed by the thread layout.
@@ -45,7 +47,8 @@ layer_norm_kernel(const float* __restrict__ x, const int* __restrict__ rows, con
 template <bool CENTRED>
 __global__ void __launch_bounds__(ROW_THREADS)
 gated_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ gate, const float* __restrict__ gate_bias,
-                      const float* __restrict__ w, const float* __restrict__ b, float eps, float* __restrict__ residual, int H) {
+                      const float* __restrict__ w, const float* __restrict__ b, float eps, float* __restrict__ residual,
+                      __nv_bfloat16* __restrict__ rounded, int H) {
     extern __shared__ float row[];          // H floats: the gated row
     __shared__ float scratch[32];
     pdl_launch_dependents();
@@ -66,14 +69,17 @@ gated_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ gat
         ss = fmaf(d, d, ss);
     }
     const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += ROW_THREADS)
-        residual[base + i] += (row[i] - mean) * rstd * w[i] + (b ? b[i] : 0.0f);
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS) {
+        const float r = residual[base + i] + ((row[i] - mean) * rstd * w[i] + (b ? b[i] : 0.0f));
+        residual[base + i] = r;
+        if (rounded) rounded[base + i] = __float2bfloat16_rn(r);      // what the next sublayer's products read
+    }
 }
 
 // ---------------------------------------------------------------------------------- per-group RMS norm with gate
 // TPG threads per (token, group): a warp for the short rows of a head, a whole block of 256 for wide groups (a
 // state-space layer normalises all its channels as one group or a few).  gate_mode 0: none; 1: out *= sigmoid(gate)
-// after the norm; 2: v *= silu(gate) before.
+// after the norm; 2: v *= silu(gate) before; 3: out *= silu(gate) after.
 template <typename TO, int TPG>
 __global__ void __launch_bounds__(256)
 group_norm_gate_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gate, int ldg,
@@ -106,8 +112,16 @@ group_norm_gate_kernel(const float* __restrict__ x, int ldx, const float* __rest
         if (gate_mode == 2) { const float z = gl[j]; v *= z * sigmoidf_(z); }
         v = v * r * wg[j];
         if (gate_mode == 1) v *= sigmoidf_(gl[j]);
+        else if (gate_mode == 3) { const float z = gl[j]; v *= z * sigmoidf_(z); }
         o[j] = from_float<TO>(v);
     }
+}
+
+__global__ void round_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16_rn(x[i]);
 }
 
 __global__ void scaled_sum_kernel(const float* __restrict__ x, float a, const float* __restrict__ y, float b,
@@ -139,7 +153,7 @@ EMBER_API int ember_layer_norm(const float* x, const int* rows, const float* w, 
 }
 
 EMBER_API int ember_gated_norm_add(const float* y, const float* gate, const float* gate_bias, const float* w, const float* b, float eps, int centred,
-                                   float* residual, int n_rows, int H, void* stream) {
+                                   float* residual, void* rounded, int n_rows, int H, void* stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || (size_t)H * 4 > 200 * 1024) return fail("gated_norm_add: width %d is not taken", H);
     cudaStream_t st = (cudaStream_t)stream;
@@ -148,8 +162,8 @@ EMBER_API int ember_gated_norm_add(const float* y, const float* gate, const floa
         cudaFuncSetAttribute(gated_norm_add_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         cudaFuncSetAttribute(gated_norm_add_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
-    if (centred) launch_kernel(gated_norm_add_kernel<true>, n_rows, ROW_THREADS, smem, st, y, gate, gate_bias, w, b, eps, residual, H);
-    else launch_kernel(gated_norm_add_kernel<false>, n_rows, ROW_THREADS, smem, st, y, gate, gate_bias, w, b, eps, residual, H);
+    if (centred) launch_kernel(gated_norm_add_kernel<true>, n_rows, ROW_THREADS, smem, st, y, gate, gate_bias, w, b, eps, residual, (__nv_bfloat16*)rounded, H);
+    else launch_kernel(gated_norm_add_kernel<false>, n_rows, ROW_THREADS, smem, st, y, gate, gate_bias, w, b, eps, residual, (__nv_bfloat16*)rounded, H);
     return check_launch("gated_norm_add");
 }
 
@@ -158,7 +172,7 @@ EMBER_API int ember_group_norm_gate(const float* x, int ldx, const float* gate, 
                                     void* stream) {
     if (T <= 0) return 0;
     if (groups <= 0 || V <= 0 || ldx < groups * V) return fail("group_norm_gate: %d groups of %d in rows of %d", groups, V, ldx);
-    if (gate_mode < 0 || gate_mode > 2 || (gate_mode && (!gate || ldg < groups * V))) return fail("group_norm_gate: bad gate");
+    if (gate_mode < 0 || gate_mode > 3 || (gate_mode && (!gate || ldg < groups * V))) return fail("group_norm_gate: bad gate");
     cudaStream_t st = (cudaStream_t)stream;
     const long long rows = (long long)T * groups;
     const bool wide = V > 512;
@@ -176,4 +190,10 @@ EMBER_API int ember_scaled_sum(const float* x, float a, const float* y, float b,
     if (n <= 0) return 0;
     launch_kernel(scaled_sum_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, x, a, y, b, out, accumulate, (size_t)n);
     return check_launch("scaled_sum");
+}
+
+EMBER_API int ember_round_rows(const float* x, void* out, long long n, void* stream) {
+    if (n <= 0) return 0;
+    launch_kernel(round_rows_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, x, (__nv_bfloat16*)out, (size_t)n);
+    return check_launch("round_rows");
 }

@@ -145,6 +145,59 @@ __global__ void delta_scan_kernel(DeltaArgs p) {
     store_tile(tile, S, D, V, j, live);
 }
 
+// ------------------------------------------------------- gated linear attention, one decay per key channel
+//   S <- diag(alpha) S + k v^T;  o = S^T q,  alpha = sigmoid(z + bias)^(1 / tau), q scaled by D^-1/2.
+// The general form (the state tile in shared memory), for more than 256 key channels.
+struct GlaArgs {
+    const float* proj; int ld; int off_q, off_k, off_v;   // [T, ...]: q, k (H D each), v (H V)
+    const float* z; int ld_z;                             // [T, H D] decay logits (before the bias)
+    const float* z_bias;                                  // [H D] or null
+    float decay_power;                                    // 1 / tau
+    float* state; long long state_stride;                 // [slot][H][D][V]
+    float* out;                                           // [T, H V]
+    const int* query_start; const int* slots;
+    int H, D, V;
+};
+
+__global__ void gla_scan_kernel(GlaArgs p) {
+    extern __shared__ float smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y, VT = blockDim.x, j = blockIdx.z * VT + threadIdx.x;
+    const int D = p.D, V = p.V;
+    const bool live = j < V;
+    float* tile = smem;                       // [D][VT]
+    float* vec = smem + (size_t)D * VT;       // 2 x (k[D], q[D], alpha[D])
+    float* S = p.state + (size_t)p.slots[s] * p.state_stride + (size_t)h * D * V;
+    load_tile(tile, S, D, V, j, live);
+    const float qscale = 1.0f / sqrtf((float)D);
+    const int first = p.query_start[s], end = p.query_start[s + 1];
+    for (int t = first; t < end; t++) {
+        const int b = (t - first) & 1;
+        float* kb = vec + b * 3 * D, *qb = kb + D, *gb = qb + D;
+        const float* row = p.proj + (size_t)t * p.ld;
+        for (int i = threadIdx.x; i < D; i += VT) {
+            kb[i] = row[p.off_k + h * D + i];
+            qb[i] = row[p.off_q + h * D + i] * qscale;
+            gb[i] = expf(logsigmoidf_(p.z[(size_t)t * p.ld_z + h * D + i] + (p.z_bias ? p.z_bias[h * D + i] : 0.0f)) * p.decay_power);
+        }
+        __syncthreads();
+        if (live) {
+            const float v = row[p.off_v + h * V + j];
+            float o = 0.0f;
+            for (int i = 0; i < D; i++) {
+                const float x = fmaf(kb[i], v, tile[i * VT + threadIdx.x] * gb[i]);
+                tile[i * VT + threadIdx.x] = x;
+                o = fmaf(x, qb[i], o);
+            }
+            p.out[(size_t)t * p.H * V + h * V + j] = o;
+        }
+    }
+    store_tile(tile, S, D, V, j, live);
+}
+
+//
+
 // ------------------------------------------------------------- matrix memory with exponential input gate
 // Per head, with log gates i~ = cap tanh((i + b_i) / cap), f~ = logsigmoid(cap tanh((f + b_f) / cap)) and a running
 // maximum m (0 for a new request):
@@ -345,7 +398,8 @@ __device__ __forceinline__ float rows_sum(float v) {
     return v;
 }
 
-// One kernel for the three recurrences (MODE 0 delta rule, 1 matrix memory, 2 state space).  A run is walked in chunks
+// One kernel for the four recurrences (MODE 0 delta rule, 1 matrix memory, 2 state space, 3 gated linear attention:
+// S <- diag(alpha) S + k v^T, o = S^T q with alpha = sigmoid(z + bias)^(1 / tau) per key channel and q times D^-1/2).  A run is walked in chunks
 // of CT tokens: while a chunk is computed from shared memory (no block-wide barrier between its tokens), the next
 // chunk's inputs are already on their way into registers; each warp then prepares its tokens of that chunk (unit
 // norms, decays, gates: a token's vector is spread over the warp's lanes, so its sums are warp sums) and stores
@@ -362,6 +416,7 @@ struct ScanArgs {
     float key_eps;
     int off_q, off_k, off_v;               // matrix memory: columns of x
     float* gates;                          // matrix memory: [T, H, 4]
+    float decay_power;                     // gated linear attention: 1 / tau
 };
 
 template <int N>
@@ -376,7 +431,7 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int NV = MODE == 0 ? 3 : 2;
+    constexpr int NV = (MODE == 0 || MODE == 3) ? 3 : 2;
     constexpr int VS = RG * (RS + 4);               // a vector in shared memory: row group r starts at r (RS + 4)
     constexpr int TOK = NV * VS + 4 + RCOLS;        // vectors, four scalars, the block's 32 column values
     constexpr int TPW = (CT + NW - 1) / NW, EPL = RG * RS / 32;   // (CT: 16 or 8 tokens a chunk for prompt portions, 1 for decode steps)
@@ -394,12 +449,12 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
     float st[RS];
     for (int i = threadIdx.x; i < 2 * CT * TOK; i += RTHREADS) chunks[i] = 0.0f;
     const int first = p.query_start[s], end = p.query_start[s + 1];
-    const float rate = MODE == 1 ? 0.0f : expf(p.A_log[h]);
+    const float rate = (MODE == 1 || MODE == 3) ? 0.0f : expf(p.A_log[h]);
     const float qscale = 1.0f / sqrtf((float)D);
     // where this head's vectors start in a row of x
-    const int off0 = MODE == 0 ? p.G * D + grp * D : (MODE == 1 ? p.off_k + h * D : H * V + grp * D);               // k | k | B
-    const int off1 = MODE == 0 ? grp * D : (MODE == 1 ? p.off_q + h * D : H * V + p.G * D + grp * D);               // q | q | C
-    const int off_col = MODE == 0 ? 2 * p.G * D + h * V : (MODE == 1 ? p.off_v + h * V : h * V);                    // v | v | x
+    const int off0 = MODE == 0 ? p.G * D + grp * D : ((MODE == 1 || MODE == 3) ? p.off_k + h * D : H * V + grp * D);               // k | k | B
+    const int off1 = MODE == 0 ? grp * D : ((MODE == 1 || MODE == 3) ? p.off_q + h * D : H * V + p.G * D + grp * D);               // q | q | C
+    const int off_col = MODE == 0 ? 2 * p.G * D + h * V : ((MODE == 1 || MODE == 3) ? p.off_v + h * V : h * V);                    // v | v | x
 
     float f0[TPW][EPL], f1[TPW][EPL], f2[TPW][EPL], fc[TPW], fs[TPW];
     auto prefetch = [&](int t0) {
@@ -414,12 +469,12 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
                 if (i < D) {
                     f0[w][m] = row[off0 + i];
                     f1[w][m] = row[off1 + i];
-                    if (MODE == 0) f2[w][m] = p.a[(size_t)t * p.ld_a + h * D + i];
+                    if (MODE == 0 || MODE == 3) f2[w][m] = p.a[(size_t)t * p.ld_a + h * D + i];
                 }
             }
             const int c = col0 + lane;
             fc[w] = c < V ? row[off_col + c] : 1.0f;
-            if (MODE != 1) fs[w] = p.b[(size_t)t * p.ld_b + h];
+            if (MODE == 0 || MODE == 2) fs[w] = p.b[(size_t)t * p.ld_b + h];
         }
     };
     auto prepare = [&](int t0, float* buf) {
@@ -435,7 +490,9 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
                 if (i < D) {
                     const int vi = i + (i / RS) * 4;
                     tok[vi] = f0[w][m];
-                    tok[VS + vi] = MODE == 1 ? f1[w][m] * qscale : f1[w][m];
+                    tok[VS + vi] = (MODE == 1 || MODE == 3) ? f1[w][m] * qscale : f1[w][m];
+                    if (MODE == 3)      // alpha = sigmoid(z)^(1 / tau) = exp(logsigmoid(z) / tau)
+                        tok[2 * VS + vi] = expf(logsigmoidf_(f2[w][m] + (p.dt_bias ? p.dt_bias[h * D + i] : 0.0f)) * p.decay_power);
                     if (MODE == 0) {
                         tok[2 * VS + vi] = expf(-rate * softplusf_(f2[w][m] + p.dt_bias[h * D + i]));
                         s0 = fmaf(f0[w][m], f0[w][m], s0); s1 = fmaf(f1[w][m], f1[w][m], s1); s01 = fmaf(f0[w][m], f1[w][m], s01);
@@ -456,7 +513,7 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
                     const float* g = p.gates + ((size_t)t * H + h) * 4;
                     tok[NV * VS + 0] = g[0]; tok[NV * VS + 1] = g[1];
                 }
-            } else if (lane == 0) {
+            } else if (MODE == 2 && lane == 0) {
                 const float dt = softplusf_(fs[w] + p.dt_bias[h]);
                 tok[NV * VS + 0] = expf(-rate * dt); tok[NV * VS + 1] = dt;
             }
@@ -484,7 +541,7 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
             for (int i4 = 0; i4 < RS / 4; i4++) {
                 x.v0[i4] = reinterpret_cast<const float4*>(tok + base)[i4];
                 x.v1[i4] = reinterpret_cast<const float4*>(tok + VS + base)[i4];
-                if (MODE == 0) x.v2[i4] = reinterpret_cast<const float4*>(tok + 2 * VS + base)[i4];
+                if (MODE == 0 || MODE == 3) x.v2[i4] = reinterpret_cast<const float4*>(tok + 2 * VS + base)[i4];
             }
         };
         auto step = [&](int tt, const TokenRegs<RS / 4>& x) {
@@ -514,6 +571,17 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
                     st[4 * i4 + 0] = fmaf(k.x, uk, st[4 * i4 + 0]); st[4 * i4 + 1] = fmaf(k.y, uk, st[4 * i4 + 1]);
                     st[4 * i4 + 2] = fmaf(k.z, uk, st[4 * i4 + 2]); st[4 * i4 + 3] = fmaf(k.w, uk, st[4 * i4 + 3]);
                 }
+            } else if (MODE == 3) {
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int i4 = 0; i4 < RS / 4; i4++) {
+                    const float4 k = x.v0[i4], q = x.v1[i4], g = x.v2[i4];
+                    st[4 * i4 + 0] = fmaf(k.x, x.val, g.x * st[4 * i4 + 0]); st[4 * i4 + 1] = fmaf(k.y, x.val, g.y * st[4 * i4 + 1]);
+                    st[4 * i4 + 2] = fmaf(k.z, x.val, g.z * st[4 * i4 + 2]); st[4 * i4 + 3] = fmaf(k.w, x.val, g.w * st[4 * i4 + 3]);
+                    acc[0] = fmaf(st[4 * i4 + 0], q.x, acc[0]); acc[1] = fmaf(st[4 * i4 + 1], q.y, acc[1]);
+                    acc[2] = fmaf(st[4 * i4 + 2], q.z, acc[2]); acc[3] = fmaf(st[4 * i4 + 3], q.w, acc[3]);
+                }
+                o = rows_sum<RG>((acc[0] + acc[1]) + (acc[2] + acc[3]));
             } else {
                 const float keep = x.sc.x, pv = x.sc.y * x.val;                 // put v | dt x
                 float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -559,7 +627,7 @@ inline bool regs_kernels_on() {
 
 template <int MODE, int RS, int CT, int RG>
 inline int launch_scan_ct(const ScanArgs& p, int S, int n_cols, cudaStream_t st) {
-    constexpr int NV = MODE == 0 ? 3 : 2;
+    constexpr int NV = (MODE == 0 || MODE == 3) ? 3 : 2;
     const size_t smem = ((size_t)RG * RS * 33 + 2 * CT * (NV * RG * (RS + 4) + 4 + RCOLS)) * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(scan_chunks_kernel<MODE, RS, CT, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -687,4 +755,27 @@ EMBER_API int ember_ssm_scan(const float* conv, int ld_conv, const float* dt, in
     }
     launch_kernel(ssm_scan_kernel, dim3(S, H, (V + VT - 1) / VT), VT, smem, (cudaStream_t)stream, p);
     return check_launch("ssm_scan");
+}
+
+EMBER_API int ember_gla_scan(const float* proj, int ld, int off_q, int off_k, int off_v, const float* z, int ld_z, const float* z_bias,
+                             float decay_power, float* state, long long state_stride, float* out, const int* query_start,
+                             const int* slots, int T, int S, int H, int D, int V, void* stream) {
+    if (S <= 0) return 0;
+    if (H <= 0 || D <= 0 || V <= 0 || !(decay_power > 0.0f)) return fail("gla_scan: %d heads of %d x %d, decay power %g", H, D, V, decay_power);
+    if (S > 65535 || H > 65535) return fail("gla_scan: too many runs or heads for one launch");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (rows_per_thread(D) && regs_kernels_on()) {
+        ScanArgs q{};
+        q.state = state; q.state_stride = state_stride; q.out = out; q.query_start = query_start; q.slots = slots;
+        q.H = H; q.G = H; q.D = D; q.V = V; q.x = proj; q.ld_x = ld; q.off_q = off_q; q.off_k = off_k; q.off_v = off_v;
+        q.a = z; q.ld_a = ld_z; q.dt_bias = z_bias; q.decay_power = decay_power;
+        if (launch_scan<3>(q, S, V, T == S, st)) return 1;
+        return check_launch("gla_scan");
+    }
+    size_t smem;
+    const int VT = pick_columns(D, V, 6 * D, &smem);
+    if (allow_smem(gla_scan_kernel, smem, "gla_scan")) return 1;
+    GlaArgs p{proj, ld, off_q, off_k, off_v, z, ld_z, z_bias, decay_power, state, state_stride, out, query_start, slots, H, D, V};
+    launch_kernel(gla_scan_kernel, dim3(S, H, (V + VT - 1) / VT), VT, smem, st, p);
+    return check_launch("gla_scan");
 }

@@ -1,0 +1,582 @@
+// Softmax attention with a sink over a paged cache, and what two mixers need around it:
+//
+//   * whole_norm_store:  q/k/v of a token with biases, one RMS norm over the whole query projection and one over the
+//     whole key projection (all heads at once), queries out, keys [.., D] and values [.., DV] into their pages;
+//   * latent_prepare:    a token's low-rank query latent (RMS norm) out, and its key/value latent (RMS norm) with the
+//     rotated shared key part behind it into the token's single cache row [c | k_rot];
+//   * rotate_pairs:      rotation of neighbouring pairs (2i, 2i + 1) of a slice of every head, fp32 in, cache type out;
+//   * head_gemm:         out[t, h, :] = W[h] x[t, h, :] for every head (a product per head, weights [H, N, K]), with an
+//     optional sigmoid gate on the result: folds a head's key up-projection into its query and takes a head's value
+//     up-projection of the attended latent;
+//   * sink_attention:    o = sum_j w_j v_j with w = softmax over the visible keys and one more term exp(sink[h]) in the
+//     denominator that has no key and no value; visible: j <= i and (no window, or i - j < window, or j < keep_first).
+//     Keys have D elements, values DV; with no value pool a value is the first DV elements of the key row (the
+//     latent serves as both).  Any number of query heads per key head.
+//
+// Scores, weights, norms, angles and sums are fp32.  Work unit of the attention: a tile of consecutive query tokens of
+// one run x a chunk of the query heads of one key head x one split of the key range; splits have a fixed length
+// anchored at key 0 and are merged in ascending order, so a token's result does not depend on the rest of the step.
+#include "common.cuh"
+
+EMBER_DEFINE_LAST_ERROR
+
+namespace ember {
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ------------------------------------------------------------------------------------ q/k/v of a windowed layer
+struct WholeNormArgs {
+    const float* qkv; int ld;          // [T, q | k | v] fp32 (no bias yet)
+    const float* bias;                 // [q | k | v] or null
+    const float* q_w; const float* k_w;   // weights over the whole projection, or null (no norm)
+    float eps;
+    int H, G, D, DV;
+    const int* positions; const int* seq_of; const int* block_table;
+    int max_blocks, page, num_pages;
+    void* q_out; void* k_pool; void* v_pool;
+    int write_kv;
+    int* err;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) whole_norm_store_kernel(WholeNormArgs p) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int QN = p.H * p.D, KN = p.G * p.D, VN = p.G * p.DV;
+    const float* row = p.qkv + (size_t)t * p.ld;
+    const float* b = p.bias;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < QN; i += blockDim.x) {
+        const float v = row[i] + (b ? b[i] : 0.0f);
+        ss = fmaf(v, v, ss);
+    }
+    const float rq = p.q_w ? 1.0f / sqrtf(block_sum(ss, scratch) / (float)QN + p.eps) : 1.0f;
+    T* qo = (T*)p.q_out + (size_t)t * QN;
+    for (int i = threadIdx.x; i < QN; i += blockDim.x) {
+        const float v = row[i] + (b ? b[i] : 0.0f);
+        qo[i] = from_float<T>(p.q_w ? v * rq * p.q_w[i] : v);
+    }
+    if (!p.write_kv) return;
+    ss = 0.0f;
+    for (int i = threadIdx.x; i < KN; i += blockDim.x) {
+        const float v = row[QN + i] + (b ? b[QN + i] : 0.0f);
+        ss = fmaf(v, v, ss);
+    }
+    const float rk = p.k_w ? 1.0f / sqrtf(block_sum(ss, scratch) / (float)KN + p.eps) : 1.0f;
+    const int pos = p.positions[t], seq = p.seq_of[t];
+    const int blk = p.block_table[(size_t)seq * p.max_blocks + pos / p.page];
+    if (blk < 0 || blk >= p.num_pages) {
+        if (threadIdx.x == 0 && p.err) atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
+        return;
+    }
+    const int in_page = pos % p.page;
+    T* kp = (T*)p.k_pool;
+    T* vp = (T*)p.v_pool;
+    for (int i = threadIdx.x; i < KN; i += blockDim.x) {
+        const int g = i / p.D, d = i - g * p.D;
+        const float v = row[QN + i] + (b ? b[QN + i] : 0.0f);
+        kp[(((size_t)blk * p.G + g) * p.page + in_page) * p.D + d] = from_float<T>(p.k_w ? v * rk * p.k_w[i] : v);
+    }
+    for (int i = threadIdx.x; i < VN; i += blockDim.x) {
+        const int g = i / p.DV, d = i - g * p.DV;
+        const float v = row[QN + KN + i] + (b ? b[QN + KN + i] : 0.0f);
+        vp[(((size_t)blk * p.G + g) * p.page + in_page) * p.DV + d] = from_float<T>(v);
+    }
+}
+
+// ------------------------------------------------------------------------------------- latents of a token
+struct LatentArgs {
+    const float* a; int ld;            // [T, ...] fp32: the fused down-projections
+    int q_col, q_rank;                 // query latent (q_rank 0: none)
+    int c_col, kv_rank, rot_dim;       // key/value latent and, behind it, the shared key part to rotate
+    const float* q_w; const float* c_w;
+    float eps;
+    const float* inv_freq; int rotary; // rotary <= rot_dim elements are rotated in neighbouring pairs
+    const int* positions; const int* seq_of; const int* block_table;
+    int max_blocks, page, num_pages;
+    void* cq_out;                      // [T, q_rank]
+    void* pool;                        // [pages, 1, page, kv_rank + rot_dim]
+    int write_kv;
+    int* err;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) latent_prepare_kernel(LatentArgs p) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float* row = p.a + (size_t)t * p.ld;
+    if (p.q_rank > 0) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) ss = fmaf(row[p.q_col + i], row[p.q_col + i], ss);
+        const float r = 1.0f / sqrtf(block_sum(ss, scratch) / (float)p.q_rank + p.eps);
+        T* o = (T*)p.cq_out + (size_t)t * p.q_rank;
+        for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) o[i] = from_float<T>(row[p.q_col + i] * r * p.q_w[i]);
+    }
+    if (!p.write_kv) return;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) ss = fmaf(row[p.c_col + i], row[p.c_col + i], ss);
+    const float r = 1.0f / sqrtf(block_sum(ss, scratch) / (float)p.kv_rank + p.eps);
+    const int pos = p.positions[t], seq = p.seq_of[t];
+    const int blk = p.block_table[(size_t)seq * p.max_blocks + pos / p.page];
+    if (blk < 0 || blk >= p.num_pages) {
+        if (threadIdx.x == 0 && p.err) atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
+        return;
+    }
+    const int W = p.kv_rank + p.rot_dim;
+    T* dst = (T*)p.pool + ((size_t)blk * p.page + pos % p.page) * W;
+    for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) dst[i] = from_float<T>(row[p.c_col + i] * r * p.c_w[i]);
+    const float* kr = row + p.c_col + p.kv_rank;
+    for (int i = threadIdx.x; i < p.rot_dim / 2 + (p.rot_dim & 1); i += blockDim.x) {
+        const int a = 2 * i, c = 2 * i + 1;
+        if (c < p.rotary) {
+            float sn, cs;
+            sincosf((float)pos * p.inv_freq[i], &sn, &cs);
+            const float u = kr[a], v = kr[c];
+            dst[p.kv_rank + a] = from_float<T>(u * cs - v * sn);
+            dst[p.kv_rank + c] = from_float<T>(v * cs + u * sn);
+        } else {
+            dst[p.kv_rank + a] = from_float<T>(kr[a]);
+            if (c < p.rot_dim) dst[p.kv_rank + c] = from_float<T>(kr[c]);
+        }
+    }
+}
+
+// out[t, h, out_col + i] = rotated in[t, h, in_col + i], i < width; pairs (2i, 2i + 1) below `rotary` turn.
+template <typename T>
+__global__ void rotate_pairs_kernel(const float* __restrict__ in, int ld_in, int in_head, int in_col, T* __restrict__ out,
+                                    int ld_out, int out_head, int out_col, int H, int width, int rotary,
+                                    const float* __restrict__ inv_freq, const int* __restrict__ positions) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int half = (width + 1) / 2;
+    const float pos = (float)positions[t];
+    for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        const float* src = in + (size_t)t * ld_in + (size_t)h * in_head + in_col;
+        T* dst = out + (size_t)t * ld_out + (size_t)h * out_head + out_col;
+        const int a = 2 * i, c = 2 * i + 1;
+        if (c < rotary) {
+            float sn, cs;
+            sincosf(pos * inv_freq[i], &sn, &cs);
+            const float u = src[a], v = src[c];
+            dst[a] = from_float<T>(u * cs - v * sn);
+            dst[c] = from_float<T>(v * cs + u * sn);
+        } else {
+            dst[a] = from_float<T>(src[a]);
+            if (c < width) dst[c] = from_float<T>(src[c]);
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------------- a product per head
+// out[t, h, n] = sum_k x[t, h, k] w[h, n, k], optionally times sigmoid(gate[t, h, n]).  Tiles of 32 tokens x 64
+// outputs, K in steps of 16; k ascends for every output, so a row's result does not depend on the rest of the step.
+constexpr int HG_BM = 32, HG_BN = 64, HG_BK = 16;
+
+struct HeadGemmArgs {
+    const float* x; int ld_x, x_head, x_col;
+    const void* w;                       // [H, N, K]
+    void* out; int ld_o, o_head, o_col;
+    const float* gate; int ld_g, g_col;  // gate[t, g_col + h N + n] or null
+    int T, H, N, K;
+};
+
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256) head_gemm_kernel(HeadGemmArgs p) {
+    __shared__ float As[HG_BK][HG_BM + 1];
+    __shared__ float Bs[HG_BK][HG_BN + 1];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.z, m0 = blockIdx.x * HG_BM, n0 = blockIdx.y * HG_BN;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // 16 x 16: outputs (ty * 2 + i, tx * 4 + j)
+    const TW* w = (const TW*)p.w + (size_t)h * p.N * p.K;
+    float acc[2][4] = {};
+    for (int k0 = 0; k0 < p.K; k0 += HG_BK) {
+        for (int idx = threadIdx.x; idx < HG_BM * HG_BK; idx += 256) {
+            const int r = idx / HG_BK, k = idx - r * HG_BK;
+            const int t = m0 + r;
+            As[k][r] = (t < p.T && k0 + k < p.K) ? p.x[(size_t)t * p.ld_x + (size_t)h * p.x_head + p.x_col + k0 + k] : 0.0f;
+        }
+        for (int idx = threadIdx.x; idx < HG_BN * HG_BK; idx += 256) {
+            const int r = idx / HG_BK, k = idx - r * HG_BK;
+            const int n = n0 + r;
+            Bs[k][r] = (n < p.N && k0 + k < p.K) ? to_float(w[(size_t)n * p.K + k0 + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < HG_BK; k++) {
+            float a[2], b[4];
+#pragma unroll
+            for (int i = 0; i < 2; i++) a[i] = As[k][ty * 2 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = Bs[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int t = m0 + ty * 2 + i;
+        if (t >= p.T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= p.N) continue;
+            float v = acc[i][j];
+            if (p.gate) v *= sigmoidf_(p.gate[(size_t)t * p.ld_g + p.g_col + (size_t)h * p.N + n]);
+            ((TO*)p.out)[(size_t)t * p.ld_o + (size_t)h * p.o_head + p.o_col + n] = from_float<TO>(v);
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------------------------- attention
+constexpr int SA_WARPS = 8;
+constexpr int SA_ROWS_PER_WARP = 4;
+constexpr int SA_MAX_ROWS = SA_WARPS * SA_ROWS_PER_WARP;   // (query, head) rows of a tile
+constexpr int SA_KT = 32;                                    // keys per shared-memory tile
+
+struct SinkAttnParams {
+    const void* q;        // [T, H, D]
+    const void* k_pool;   // [pages][G][page][D]
+    const void* v_pool;   // [pages][G][page][DV], or null: a value is the first DV elements of the key row
+    void* out;            // [T, H, DV]
+    float* part_o;        // [T, H, n_splits, DV]   (n_splits > 1)
+    float* part_ml;       // [T, H, n_splits, 2]
+    const int* tiles;     // [n_tiles, 4] = (run, first token row, queries, position of the first query)
+    const int* block_table;
+    const float* sink;    // [H] or null
+    int max_blocks, page, num_pages;
+    int H, G, D, DV;
+    int head_chunk;       // query heads of one key head a block takes (tile_q * head_chunk <= SA_MAX_ROWS)
+    int window, keep_first;
+    float scale;
+    int n_splits, split_keys;
+    int* err;
+};
+
+template <typename T, typename TO, int NC>
+__global__ void __launch_bounds__(SA_WARPS * 32)
+sink_attention_kernel(SinkAttnParams p) {
+    extern __shared__ float smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int D = p.D, DV = p.DV, DP = D + 1;
+    const bool alias = p.v_pool == nullptr;
+    float* Ks = smem;                                   // [KT][D + 1]
+    float* Vs = alias ? Ks : Ks + SA_KT * DP;           // [KT][DV] (or the key rows themselves)
+    const int vs_ld = alias ? DP : DV;
+    float* Qs = alias ? Ks + SA_KT * DP : Vs + SA_KT * DV;   // [rows][D]
+
+    const int group = p.H / p.G;
+    const int chunks = (group + p.head_chunk - 1) / p.head_chunk;
+    const int tile = blockIdx.x, kvh = blockIdx.y / chunks, hc = blockIdx.y - kvh * chunks, split = blockIdx.z;
+    const int head0 = kvh * group + hc * p.head_chunk;
+    const int nh = min(p.head_chunk, group - hc * p.head_chunk);
+    const int seq = p.tiles[tile * 4 + 0], row0 = p.tiles[tile * 4 + 1], nq = p.tiles[tile * 4 + 2],
+              pos0 = p.tiles[tile * 4 + 3];
+    const int rows = nq * nh;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* q = (const T*)p.q;
+    const T* kp = (const T*)p.k_pool;
+    const T* vp = (const T*)p.v_pool;
+
+    for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
+        const int r = idx / D, d = idx - r * D;
+        const int qi = r / nh, g = r - qi * nh;
+        Qs[r * D + d] = to_float(q[((size_t)(row0 + qi) * p.H + head0 + g) * D + d]);
+    }
+
+    // visible keys of the tile: [0, kept) and [lo, hi); with a split, their part inside the split
+    int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    int hi = pos0 + nq;
+    int kept = p.window > 0 ? min(p.keep_first, lo) : 0;
+    int s_lo = 0, s_hi = hi;
+    if (p.n_splits > 1) {
+        s_lo = split * p.split_keys;
+        s_hi = min(hi, (split + 1) * p.split_keys);
+    }
+
+    float m[SA_ROWS_PER_WARP], l[SA_ROWS_PER_WARP], acc[SA_ROWS_PER_WARP][NC];
+#pragma unroll
+    for (int i = 0; i < SA_ROWS_PER_WARP; i++) {
+        m[i] = -INFINITY;
+        l[i] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < NC; c++) acc[i][c] = 0.0f;
+    }
+
+    const int* bt = p.block_table + (size_t)seq * p.max_blocks;
+    for (int part = 0; part < 2; part++) {
+        const int a = max(part == 0 ? 0 : lo, s_lo), b = min(part == 0 ? kept : hi, s_hi);
+        if (a >= b) continue;
+        for (int k0 = a - (a % SA_KT); k0 < b; k0 += SA_KT) {
+            __syncthreads();  // the previous tile is consumed (and the queries are written before the first use)
+            for (int idx = threadIdx.x; idx < SA_KT * D; idx += blockDim.x) {
+                const int j = idx / D, d = idx - j * D;
+                const int key = k0 + j;
+                float kv = 0.0f;
+                if (key >= a && key < b) {
+                    const int blk = bt[key / p.page];
+                    if (blk >= 0 && blk < p.num_pages) {
+                        kv = to_float(kp[(((size_t)blk * p.G + kvh) * p.page + (key % p.page)) * D + d]);
+                    } else if (d == 0 && p.err) {
+                        atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
+                    }
+                }
+                Ks[j * DP + d] = kv;
+            }
+            if (!alias) {
+                for (int idx = threadIdx.x; idx < SA_KT * DV; idx += blockDim.x) {
+                    const int j = idx / DV, d = idx - j * DV;
+                    const int key = k0 + j;
+                    float vv = 0.0f;
+                    if (key >= a && key < b) {
+                        const int blk = bt[key / p.page];
+                        if (blk >= 0 && blk < p.num_pages)
+                            vv = to_float(vp[(((size_t)blk * p.G + kvh) * p.page + (key % p.page)) * DV + d]);
+                    }
+                    Vs[j * DV + d] = vv;
+                }
+            }
+            __syncthreads();
+
+#pragma unroll
+            for (int i = 0; i < SA_ROWS_PER_WARP; i++) {
+                const int r = warp + i * SA_WARPS;
+                if (r >= rows) continue;  // uniform per warp
+                const int qpos = pos0 + r / nh;
+                const int key = k0 + lane;
+                const bool visible = key >= a && key < b && key <= qpos &&
+                                     (p.window <= 0 || qpos - key < p.window || key < p.keep_first);
+                float s = 0.0f;
+                const float* qr = Qs + r * D;
+                const float* kr = Ks + lane * DP;
+                for (int d = 0; d < D; d++) s = fmaf(qr[d], kr[d], s);
+                s = visible ? s * p.scale : -INFINITY;
+                const float tmax = warp_max(s);
+                const float m_new = fmaxf(m[i], tmax);
+                if (m_new == -INFINITY) continue;  // nothing visible so far (uniform per warp)
+                const float corr = expf(m[i] - m_new);
+                const float pj = visible ? expf(s - m_new) : 0.0f;
+                l[i] = l[i] * corr + warp_sum(pj);
+                m[i] = m_new;
+#pragma unroll
+                for (int c = 0; c < NC; c++) acc[i][c] *= corr;
+                for (int j = 0; j < SA_KT; j++) {
+                    const float w = __shfl_sync(0xffffffffu, pj, j);
+                    const float* vr = Vs + j * vs_ld;
+#pragma unroll
+                    for (int c = 0; c < NC; c++) {
+                        const int d = lane + 32 * c;
+                        if (d < DV) acc[i][c] = fmaf(w, vr[d], acc[i][c]);
+                    }
+                }
+            }
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < SA_ROWS_PER_WARP; i++) {
+        const int r = warp + i * SA_WARPS;
+        if (r >= rows) continue;
+        const int qi = r / nh, g = r - qi * nh;
+        const int head = head0 + g;
+        const size_t th = (size_t)(row0 + qi) * p.H + head;
+        if (p.n_splits <= 1) {
+            // the sink joins the denominator once: it has no key and no value
+            float mm = m[i], ll = l[i], corr = 1.0f;
+            if (p.sink) {
+                const float sk = p.sink[head];
+                mm = fmaxf(m[i], sk);
+                corr = expf(m[i] - mm);
+                ll = l[i] * corr + expf(sk - mm);
+            }
+            const float inv = ll > 0.0f ? corr / ll : 0.0f;
+            TO* o = (TO*)p.out + th * DV;
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                const int d = lane + 32 * c;
+                if (d < DV) o[d] = from_float<TO>(acc[i][c] * inv);
+            }
+        } else {
+            float* po = p.part_o + (th * p.n_splits + split) * DV;
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                const int d = lane + 32 * c;
+                if (d < DV) po[d] = acc[i][c];
+            }
+            if (lane == 0) {
+                float* ml = p.part_ml + (th * p.n_splits + split) * 2;
+                ml[0] = m[i];
+                ml[1] = l[i];
+            }
+        }
+    }
+}
+
+// Merges the splits of one (token, head) in ascending order; the sink joins here.
+template <typename TO>
+__global__ void sink_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    const float* __restrict__ sink, TO* __restrict__ out, int n_splits, int DV, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t th = blockIdx.x;
+    const float* ml = part_ml + th * n_splits * 2;
+    float M = sink ? sink[th % H] : -INFINITY;
+    for (int s = 0; s < n_splits; s++) M = fmaxf(M, ml[2 * s]);
+    float L = sink ? expf(sink[th % H] - M) : 0.0f;
+    for (int s = 0; s < n_splits; s++) {
+        const float ms = ml[2 * s];
+        if (ms != -INFINITY) L += ml[2 * s + 1] * expf(ms - M);
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int d = threadIdx.x; d < DV; d += blockDim.x) {
+        float o = 0.0f;
+        for (int s = 0; s < n_splits; s++) {
+            const float ms = ml[2 * s];
+            if (ms != -INFINITY) o = fmaf(part_o[(th * n_splits + s) * DV + d], expf(ms - M), o);
+        }
+        out[th * DV + d] = from_float<TO>(o * inv);
+    }
+}
+
+template <typename T, typename TO>
+int launch_sink_attention(const SinkAttnParams& p, int n_tiles, int T_tokens, cudaStream_t st) {
+    const int D = p.D, DV = p.DV;
+    const bool alias = p.v_pool == nullptr;
+    const size_t smem = ((size_t)SA_KT * (D + 1) + (alias ? 0 : (size_t)SA_KT * DV) + (size_t)SA_MAX_ROWS * D) * sizeof(float);
+    if (smem > 220 * 1024) return fail("sink_attention: heads of %d / %d need %zu bytes of shared memory", D, DV, smem);
+    const int group = p.H / p.G, chunks = (group + p.head_chunk - 1) / p.head_chunk;
+    dim3 grid(n_tiles, p.G * chunks, p.n_splits);
+    const int nc = (DV + 31) / 32;
+    auto run = [&](auto kernel) -> int {
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return fail("sink_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
+        }
+        launch_kernel(kernel, grid, SA_WARPS * 32, smem, st, p);
+        return check_launch("sink_attention");
+    };
+    int rc;
+    if (nc <= 1) rc = run(sink_attention_kernel<T, TO, 1>);
+    else if (nc <= 2) rc = run(sink_attention_kernel<T, TO, 2>);
+    else if (nc <= 4) rc = run(sink_attention_kernel<T, TO, 4>);
+    else if (nc <= 8) rc = run(sink_attention_kernel<T, TO, 8>);
+    else rc = run(sink_attention_kernel<T, TO, 16>);
+    if (rc) return rc;
+    if (p.n_splits > 1) {
+        launch_kernel(sink_combine_kernel<TO>, (unsigned)((size_t)T_tokens * p.H), DV >= 128 ? 128 : 64, 0, st,
+                      (const float*)p.part_o, (const float*)p.part_ml, p.sink, (TO*)p.out, p.n_splits, DV, p.H);
+        return check_launch("sink_combine");
+    }
+    return 0;
+}
+
+}  // namespace ember
+
+using namespace ember;
+
+EMBER_API int ember_whole_norm_store(const float* qkv, int ld, const float* bias, const float* q_w, const float* k_w, float eps,
+                                     int T, int H, int G, int D, int DV, const int* positions, const int* seq_of,
+                                     const int* block_table, int max_blocks, int page, int num_pages, void* q_out,
+                                     void* k_pool, void* v_pool, int dtype, int write_kv, int* err, void* stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || G <= 0 || D <= 0 || DV <= 0 || ld < H * D + G * D + G * DV)
+        return fail("whole_norm_store: %d/%d heads of %d/%d in rows of %d", H, G, D, DV, ld);
+    if (page <= 0 || max_blocks <= 0 || num_pages <= 0) return fail("whole_norm_store: bad cache geometry");
+    WholeNormArgs p{qkv, ld, bias, q_w, k_w, eps, H, G, D, DV, positions, seq_of, block_table, max_blocks, page, num_pages,
+                    q_out, k_pool, v_pool, write_kv, err};
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == EMBER_F32) launch_kernel(whole_norm_store_kernel<float>, T, 256, 0, st, p);
+    else if (dtype == EMBER_BF16) launch_kernel(whole_norm_store_kernel<__nv_bfloat16>, T, 256, 0, st, p);
+    else return fail("whole_norm_store: unsupported dtype %d", dtype);
+    return check_launch("whole_norm_store");
+}
+
+EMBER_API int ember_latent_prepare(const float* a, int ld, int q_col, int q_rank, int c_col, int kv_rank, int rot_dim,
+                                   const float* q_w, const float* c_w, float eps, const float* inv_freq, int rotary, int T,
+                                   const int* positions, const int* seq_of, const int* block_table, int max_blocks, int page,
+                                   int num_pages, void* cq_out, void* pool, int dtype, int write_kv, int* err, void* stream) {
+    if (T <= 0) return 0;
+    if (q_rank < 0 || kv_rank <= 0 || rot_dim < 0 || rotary < 0 || rotary > rot_dim || (rotary & 1))
+        return fail("latent_prepare: ranks %d / %d, rotated part %d of %d", q_rank, kv_rank, rotary, rot_dim);
+    if (write_kv && (page <= 0 || max_blocks <= 0 || num_pages <= 0)) return fail("latent_prepare: bad cache geometry");
+    if (rotary > 0 && !inv_freq) return fail("latent_prepare: a rotation needs its frequencies");
+    LatentArgs p{a, ld, q_col, q_rank, c_col, kv_rank, rot_dim, q_w, c_w, eps, inv_freq, rotary, positions, seq_of, block_table,
+                 max_blocks, page, num_pages, cq_out, pool, write_kv, err};
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == EMBER_F32) launch_kernel(latent_prepare_kernel<float>, T, 256, 0, st, p);
+    else if (dtype == EMBER_BF16) launch_kernel(latent_prepare_kernel<__nv_bfloat16>, T, 256, 0, st, p);
+    else return fail("latent_prepare: unsupported dtype %d", dtype);
+    return check_launch("latent_prepare");
+}
+
+EMBER_API int ember_rotate_pairs(const float* in, int ld_in, int in_head, int in_col, void* out, int ld_out, int out_head,
+                                 int out_col, int dtype, int T, int H, int width, int rotary, const float* inv_freq,
+                                 const int* positions, void* stream) {
+    if (T <= 0 || width <= 0) return 0;
+    if (rotary < 0 || rotary > width || (rotary & 1) || (rotary > 0 && !inv_freq)) return fail("rotate_pairs: %d of %d rotated", rotary, width);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == EMBER_F32)
+        launch_kernel(rotate_pairs_kernel<float>, T, 128, 0, st, in, ld_in, in_head, in_col, (float*)out, ld_out, out_head, out_col, H,
+                      width, rotary, inv_freq, positions);
+    else if (dtype == EMBER_BF16)
+        launch_kernel(rotate_pairs_kernel<__nv_bfloat16>, T, 128, 0, st, in, ld_in, in_head, in_col, (__nv_bfloat16*)out, ld_out,
+                      out_head, out_col, H, width, rotary, inv_freq, positions);
+    else return fail("rotate_pairs: unsupported dtype %d", dtype);
+    return check_launch("rotate_pairs");
+}
+
+EMBER_API int ember_head_gemm(const float* x, int ld_x, int x_head, int x_col, const void* w, int w_dtype, void* out, int out_dtype,
+                              int ld_o, int o_head, int o_col, const float* gate, int ld_g, int g_col, int T, int H, int N, int K,
+                              void* stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || N <= 0 || K <= 0 || H > 65535) return fail("head_gemm: %d heads of %d x %d", H, N, K);
+    HeadGemmArgs p{x, ld_x, x_head, x_col, w, out, ld_o, o_head, o_col, gate, ld_g, g_col, T, H, N, K};
+    dim3 grid((T + HG_BM - 1) / HG_BM, (N + HG_BN - 1) / HG_BN, H);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (w_dtype == EMBER_F32 && out_dtype == EMBER_F32) launch_kernel(head_gemm_kernel<float, float>, grid, 256, 0, st, p);
+    else if (w_dtype == EMBER_BF16 && out_dtype == EMBER_BF16) launch_kernel(head_gemm_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, st, p);
+    else if (w_dtype == EMBER_BF16 && out_dtype == EMBER_F32) launch_kernel(head_gemm_kernel<__nv_bfloat16, float>, grid, 256, 0, st, p);
+    else return fail("head_gemm: unsupported dtypes %d -> %d", w_dtype, out_dtype);
+    return check_launch("head_gemm");
+}
+
+// Query heads of one key head that a block takes, and the query tokens of a tile that go with it.
+EMBER_API int ember_sink_attention_head_chunk(int group) { return group <= 0 ? 0 : (group < SA_MAX_ROWS ? group : SA_MAX_ROWS); }
+
+EMBER_API int ember_sink_attention(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype, int out_f32,
+                                   int T_tokens, int H, int G, int D, int DV, const int* tiles, int n_tiles, int tile_q,
+                                   const int* block_table, int max_blocks, int page, int num_pages, int window,
+                                   int keep_first, const float* sink, float scale, int n_splits, int split_keys,
+                                   float* part_o, float* part_ml, int* err, void* stream) {
+    if (n_tiles <= 0 || T_tokens <= 0) return 0;
+    if (D <= 0 || DV <= 0 || DV > 512 || (!v_pool && DV > D)) return fail("sink_attention: heads of %d / %d are not taken", D, DV);
+    if (H <= 0 || G <= 0 || H % G) return fail("sink_attention: %d heads do not divide into %d groups", H, G);
+    const int chunk = ember_sink_attention_head_chunk(H / G);
+    if (tile_q <= 0 || tile_q * chunk > SA_MAX_ROWS) return fail("sink_attention: tiles of %d queries x %d heads exceed %d rows", tile_q, chunk, SA_MAX_ROWS);
+    if (n_splits < 1 || (n_splits > 1 && (split_keys <= 0 || !part_o || !part_ml)))
+        return fail("sink_attention: bad split configuration (%d splits of %d keys)", n_splits, split_keys);
+    if (n_splits > 65535 || (long long)G * ((H / G + chunk - 1) / chunk) > 65535) return fail("sink_attention: grid too large");
+    if (page <= 0 || max_blocks <= 0 || num_pages <= 0) return fail("sink_attention: bad cache geometry");
+    if (window < 0 || keep_first < 0) return fail("sink_attention: window %d, kept first tokens %d", window, keep_first);
+    SinkAttnParams p;
+    p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.out = out; p.part_o = part_o; p.part_ml = part_ml;
+    p.tiles = tiles; p.block_table = block_table; p.sink = sink; p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages;
+    p.H = H; p.G = G; p.D = D; p.DV = DV; p.head_chunk = chunk; p.window = window; p.keep_first = keep_first; p.scale = scale;
+    p.n_splits = n_splits; p.split_keys = split_keys; p.err = err;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == EMBER_F32) return launch_sink_attention<float, float>(p, n_tiles, T_tokens, st);
+    if (dtype == EMBER_BF16)
+        return out_f32 ? launch_sink_attention<__nv_bfloat16, float>(p, n_tiles, T_tokens, st)
+                       : launch_sink_attention<__nv_bfloat16, __nv_bfloat16>(p, n_tiles, T_tokens, st);
+    return fail("sink_attention: unsupported dtype %d", dtype);
+}

@@ -110,6 +110,7 @@ class CausalLM:
             owner = e.cache_of if e.cache_of >= 0 else e.layer
             block = self.blocks[e.layer]
             caches = {sub: storage.layer(self.cache_id(owner, sub)) for sub in self._cache_subs[e.layer]}
+            ctx.memo["schedule.index"] = i            # (a block may leave something for the run right after it)
             block.forward(ctx, h, caches, owns_cache=(owner == e.layer))
             if capture is not None:
                 capture[1][i + 1].copy_(h[row])

@@ -581,9 +581,9 @@ def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
 
 def gated_norm_add(y: torch.Tensor, gate_logits: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
                    eps: float, centred: bool, residual: torch.Tensor, n_rows: int, gate_bias: Optional[torch.Tensor] = None,
-                   stream: Optional[int] = None) -> None:
+                   rounded: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
     """residual[r] += norm(y[r] * sigmoid(gate_logits[r] + gate_bias)): a layer norm (``centred``) or an RMS norm,
-    all fp32."""
+    all fp32.  ``rounded`` (bfloat16, the residual's shape) also receives the new rows, rounded once."""
     for t, n in ((y, "y"), (weight, "weight"), (residual, "residual")):
         _check(t, n, torch.float32)
     H = residual.shape[-1]
@@ -598,11 +598,25 @@ def gated_norm_add(y: torch.Tensor, gate_logits: Optional[torch.Tensor], weight:
         _check(gate_bias, "gate_bias", torch.float32)
         if gate_bias.numel() != H:
             raise KernelError("gated_norm_add: the gate's bias does not fit the rows")
+    if rounded is not None:
+        _check(rounded, "rounded", torch.bfloat16)
+        if rounded.shape[-1] != H or rounded.numel() < n_rows * H:
+            raise KernelError("gated_norm_add: the rounded copy does not fit the rows")
     _call(lib, lib.ember_gated_norm_add, _p(y), _p(gate_logits), _p(gate_bias), _p(weight), _p(bias), c_float(eps), c_int(1 if centred else 0),
-          _p(residual), c_int(n_rows), c_int(H), _stream(stream))
+          _p(residual), _p(rounded), c_int(n_rows), c_int(H), _stream(stream))
 
 
-GATE_NONE, GATE_SIGMOID_AFTER, GATE_SILU_BEFORE = 0, 1, 2
+def round_rows(x: torch.Tensor, out: torch.Tensor, n: int, stream: Optional[int] = None) -> None:
+    """out[:n] = bfloat16(x[:n]) (fp32 in): what a sublayer that reads the residual stream itself multiplies."""
+    _check(x, "x", torch.float32)
+    _check(out, "out", torch.bfloat16)
+    if x.numel() < n or out.numel() < n:
+        raise KernelError("round_rows: a buffer is too small")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_round_rows, _p(x), _p(out), c_longlong(n), _stream(stream))
+
+
+GATE_NONE, GATE_SIGMOID_AFTER, GATE_SILU_BEFORE, GATE_SILU_AFTER = 0, 1, 2, 3
 
 
 def group_norm_gate(x: torch.Tensor, x_col: int, gate: Optional[torch.Tensor], gate_col: int, weight: torch.Tensor,
@@ -610,7 +624,7 @@ def group_norm_gate(x: torch.Tensor, x_col: int, gate: Optional[torch.Tensor], g
                     den: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
     """A token's ``groups * width`` values (fp32, from column ``x_col`` of x's rows), each group divided by its root
     mean square and multiplied by ``weight`` (one for all groups or one per group); the gate (fp32 rows, from column
-    ``gate_col``) is a sigmoid after the norm or a silu before it.  ``den`` (fp32 [T, groups, 4], what ``memory_scan``
+    ``gate_col``) is a sigmoid or a silu after the norm, or a silu before it.  ``den`` (fp32 [T, groups, 4], what ``memory_scan``
     leaves): every group is first divided by max(|den[.., 3]|, den[.., 2]) + 1e-6."""
     _check(x, "x", torch.float32)
     _check(weight, "weight", torch.float32)
@@ -789,3 +803,254 @@ def sigmoid_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     _call(lib, lib.ember_sigmoid_attention, _p(q), _p(k_pool), _p(v_pool), _p(out), c_int(dtype_code(q.dtype)), c_int(heads),
           c_int(kv_heads), c_int(dim), c_int(vdim), _p(tiles), c_int(n_tiles), _p(block_table), c_int(block_table.shape[-1]),
           c_int(page), c_int(k_pool.shape[0]), c_float(scale), _p(head_bias), _p(err), _stream(stream))
+
+
+def gla_scan(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, z: torch.Tensor, z_col: int, z_bias: Optional[torch.Tensor],
+             decay_power: float, state: torch.Tensor, out: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor,
+             T: int, S: int, heads: int, dim: int, vdim: int, stream: Optional[int] = None) -> None:
+    """Gated linear attention over the step's runs: S <- diag(alpha) S + k v^T, o = S^T q per head, with
+    alpha = sigmoid(z + z_bias)^decay_power per key channel and q times dim^-1/2.  ``proj`` fp32 [T, ld] holds q, k, v at
+    the given columns, ``z`` fp32 rows hold the decay logits [heads dim] from column z_col; the state
+    [slots, >= heads dim vdim] fp32 is read and left updated; out fp32 [T, heads vdim]."""
+    for t, n in ((proj, "proj"), (z, "z"), (state, "state"), (out, "out")) + (((z_bias, "z_bias"),) if z_bias is not None else ()):
+        _check(t, n, torch.float32)
+    _check_runs(query_start, slots, S)
+    ld = proj.shape[1]
+    if max(off_q, off_k) + heads * dim > ld or off_v + heads * vdim > ld or z_col + heads * dim > z.shape[1] or \
+            state.dim() != 2 or state.shape[1] < heads * dim * vdim or out.numel() < T * heads * vdim or \
+            (z_bias is not None and z_bias.numel() != heads * dim):
+        raise KernelError("gla_scan: buffers do not fit the head geometry")
+    lib = _lib("recurrent")
+    _call(lib, lib.ember_gla_scan, _p(proj), c_int(ld), c_int(off_q), c_int(off_k), c_int(off_v), _off(z, z_col), c_int(z.shape[1]),
+          _p(z_bias), c_float(decay_power), _p(state), c_longlong(state.shape[1]), _p(out), _p(query_start), _p(slots), c_int(T),
+          c_int(S), c_int(heads), c_int(dim), c_int(vdim), _stream(stream))
+
+
+# ------------------------------------- softmax attention with a sink, whole-projection norms, latents (csrc/sink_attention.cu)
+SINK_ATTENTION_ROWS = 32         # (query, head) rows of a tile of the kernel (its SA_MAX_ROWS)
+
+
+def sink_attention_tile_queries(group: int) -> int:
+    """Query tokens per tile: a block takes up to 32 (token, head) rows over up to 32 of the query heads of a key head."""
+    return max(1, SINK_ATTENTION_ROWS // max(1, min(group, SINK_ATTENTION_ROWS)))
+
+
+def _check_pages(k_pool, v_pool, kv_heads, page, dim, vdim, what):
+    if k_pool.dim() != 4 or tuple(k_pool.shape[1:]) != (kv_heads, page, dim) or \
+            (v_pool is not None and (tuple(v_pool.shape[1:]) != (kv_heads, page, vdim) or v_pool.shape[0] != k_pool.shape[0])):
+        raise KernelError(f"{what}: pools {tuple(k_pool.shape)} / {tuple(v_pool.shape) if v_pool is not None else None} do not fit "
+                          f"[pages, {kv_heads}, {page}, {dim} | {vdim}]")
+
+
+def whole_norm_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                     eps: float, T: int, heads: int, kv_heads: int, dim: int, vdim: int, positions: torch.Tensor,
+                     seq_of: torch.Tensor, block_table: torch.Tensor, page: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                     q_out: torch.Tensor, write_kv: bool = True, err: Optional[torch.Tensor] = None,
+                     stream: Optional[int] = None) -> None:
+    """``qkv`` fp32 [T, q | k | v] (+ ``bias``): one RMS norm over the whole query projection (weight ``q_w`` of heads x
+    dim) and one over the whole key projection, queries to ``q_out``, keys [.., dim] and values [.., vdim] to pages."""
+    _check(qkv, "qkv", torch.float32)
+    _check(q_out, "q_out")
+    _check(k_pool, "k_pool", q_out.dtype)
+    _check(v_pool, "v_pool", q_out.dtype)
+    for t, n in ((positions, "positions"), (seq_of, "seq_of"), (block_table, "block_table")):
+        _check(t, n, torch.int32)
+    qn, kn, vn = heads * dim, kv_heads * dim, kv_heads * vdim
+    for t, n, size in ((bias, "bias", qn + kn + vn), (q_w, "q_w", qn), (k_w, "k_w", kn)):
+        if t is not None:
+            _check(t, n, torch.float32)
+            if t.numel() != size:
+                raise KernelError(f"whole_norm_store: {n} has {t.numel()} elements, not {size}")
+    _check_pages(k_pool, v_pool, kv_heads, page, dim, vdim, "whole_norm_store")
+    if qkv.shape[0] < T or qkv.shape[1] < qn + kn + vn or q_out.numel() < T * qn:
+        raise KernelError("whole_norm_store: buffers too small for the step")
+    lib = _lib("sink_attention")
+    _call(lib, lib.ember_whole_norm_store, _p(qkv), c_int(qkv.shape[1]), _p(bias), _p(q_w), _p(k_w), c_float(eps), c_int(T),
+          c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), _p(positions), _p(seq_of), _p(block_table),
+          c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), _p(q_out), _p(k_pool), _p(v_pool),
+          c_int(dtype_code(q_out.dtype)), c_int(1 if write_kv else 0), _p(err), _stream(stream))
+
+
+def latent_prepare(a: torch.Tensor, q_col: int, q_rank: int, c_col: int, kv_rank: int, rot_dim: int, q_w: Optional[torch.Tensor],
+                   c_w: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rotary: int, T: int,
+                   positions: torch.Tensor, seq_of: torch.Tensor, block_table: torch.Tensor, page: int, cq_out: torch.Tensor,
+                   pool: Optional[torch.Tensor], write_kv: bool = True, err: Optional[torch.Tensor] = None,
+                   stream: Optional[int] = None) -> None:
+    """From the fused down-projections ``a`` fp32 [T, ld]: the query latent (columns q_col.., RMS norm with ``q_w``) to
+    ``cq_out`` [T, q_rank]; with ``write_kv`` the key/value latent (columns c_col.., RMS norm with ``c_w``) and behind it
+    the shared key part (rot_dim columns, the first ``rotary`` rotated in neighbouring pairs) into the token's cache
+    row [kv_rank + rot_dim] of ``pool`` [pages, 1, page, kv_rank + rot_dim]."""
+    _check(a, "a", torch.float32)
+    _check(cq_out, "cq_out")
+    for t, n in ((positions, "positions"), (seq_of, "seq_of"), (block_table, "block_table")):
+        _check(t, n, torch.int32)
+    for t, n in ((q_w, "q_w"), (c_w, "c_w"), (inv_freq, "inv_freq")):
+        if t is not None:
+            _check(t, n, torch.float32)
+    if a.shape[0] < T or q_col + q_rank > a.shape[1] or cq_out.numel() < T * q_rank or (q_rank and (q_w is None or q_w.numel() != q_rank)):
+        raise KernelError("latent_prepare: the query latent does not fit")
+    if write_kv:
+        _check(pool, "pool", cq_out.dtype)
+        if c_col + kv_rank + rot_dim > a.shape[1] or c_w is None or c_w.numel() != kv_rank or \
+                pool.dim() != 4 or tuple(pool.shape[1:]) != (1, page, kv_rank + rot_dim):
+            raise KernelError("latent_prepare: the key/value latent does not fit its pages")
+        if rotary and (inv_freq is None or inv_freq.numel() * 2 != rotary):
+            raise KernelError(f"latent_prepare: frequencies for a rotation of {rotary}")
+    lib = _lib("sink_attention")
+    _call(lib, lib.ember_latent_prepare, _p(a), c_int(a.shape[1]), c_int(q_col), c_int(q_rank), c_int(c_col), c_int(kv_rank),
+          c_int(rot_dim), _p(q_w), _p(c_w), c_float(eps), _p(inv_freq), c_int(rotary if write_kv else 0), c_int(T), _p(positions),
+          _p(seq_of), _p(block_table), c_int(block_table.shape[-1]), c_int(page), c_int(pool.shape[0] if pool is not None else 1),
+          _p(cq_out), _p(pool), c_int(dtype_code(cq_out.dtype)), c_int(1 if write_kv else 0), _p(err), _stream(stream))
+
+
+def rotate_pairs(x: torch.Tensor, x_head: int, x_col: int, out: torch.Tensor, out_head: int, out_col: int, T: int, heads: int,
+                 width: int, rotary: int, inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
+                 stream: Optional[int] = None) -> None:
+    """out[t, h, out_col + i] = x[t, h, x_col + i] for i < width, with pairs (2i, 2i + 1) below ``rotary`` turned by
+    float(position) * inv_freq[i]; x fp32 rows of heads ``x_head`` apart, out rows of heads ``out_head`` apart."""
+    _check(x, "x", torch.float32)
+    _check(out, "out")
+    _check(positions, "positions", torch.int32)
+    if inv_freq is not None:
+        _check(inv_freq, "inv_freq", torch.float32)
+    if rotary and (inv_freq is None or inv_freq.numel() * 2 != rotary):
+        raise KernelError(f"rotate_pairs: frequencies for a rotation of {rotary}")
+    if x.shape[0] < T or out.shape[0] < T or (heads - 1) * x_head + x_col + width > x.shape[1] or \
+            (heads - 1) * out_head + out_col + width > out.shape[1]:
+        raise KernelError("rotate_pairs: the slices do not fit their rows")
+    lib = _lib("sink_attention")
+    _call(lib, lib.ember_rotate_pairs, _p(x), c_int(x.shape[1]), c_int(x_head), c_int(x_col), _p(out), c_int(out.shape[1]),
+          c_int(out_head), c_int(out_col), c_int(dtype_code(out.dtype)), c_int(T), c_int(heads), c_int(width), c_int(rotary),
+          _p(inv_freq), _p(positions), _stream(stream))
+
+
+def head_gemm(x: torch.Tensor, x_head: int, x_col: int, w: torch.Tensor, out: torch.Tensor, out_head: int, out_col: int, T: int,
+              gate: Optional[torch.Tensor] = None, gate_col: int = 0, stream: Optional[int] = None) -> None:
+    """out[t, h, out_col + n] = sum_k x[t, h, x_col + k] * w[h, n, k], a product per head (``w`` [heads, N, K]); with
+    ``gate`` (fp32 rows) the result is multiplied by sigmoid(gate[t, gate_col + h N + n]).  x fp32 2-D."""
+    _check(x, "x", torch.float32)
+    _check(w, "w")
+    _check(out, "out")
+    H, N, K = w.shape
+    if x.shape[0] < T or out.shape[0] < T or (H - 1) * x_head + x_col + K > x.shape[1] or (H - 1) * out_head + out_col + N > out.shape[1]:
+        raise KernelError(f"head_gemm: {H} heads of {N} x {K} do not fit rows of {x.shape[1]} -> {out.shape[1]}")
+    if gate is not None:
+        _check(gate, "gate", torch.float32)
+        if gate.shape[0] < T or gate_col + H * N > gate.shape[1]:
+            raise KernelError("head_gemm: the gate does not fit")
+    lib = _lib("sink_attention")
+    _call(lib, lib.ember_head_gemm, _p(x), c_int(x.shape[1]), c_int(x_head), c_int(x_col), _p(w), c_int(dtype_code(w.dtype)), _p(out),
+          c_int(dtype_code(out.dtype)), c_int(out.shape[1]), c_int(out_head), c_int(out_col), _p(gate),
+          c_int(gate.shape[1] if gate is not None else 0), c_int(gate_col), c_int(T), c_int(H), c_int(N), c_int(K), _stream(stream))
+
+
+def sink_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch.Tensor], out: torch.Tensor, T: int, heads: int,
+                   kv_heads: int, dim: int, vdim: int, tiles: torch.Tensor, n_tiles: int, tile_q: int, block_table: torch.Tensor,
+                   page: int, window: int, keep_first: int, sink: Optional[torch.Tensor], scale: float, n_splits: int = 1,
+                   split_keys: int = 0, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                   err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """out[t, h] = sum_j w_j v_j over the visible keys j <= t (under a window: t - j < window or j < keep_first), w the
+    softmax of scale * q . k_j whose denominator also holds exp(sink[h]).  Keys [.., dim], values [.., vdim]; without
+    ``v_pool`` a value is the first ``vdim`` elements of the key row.  ``out`` is q's dtype or float32."""
+    _check(q, "q")
+    _check(k_pool, "k_pool", q.dtype)
+    if v_pool is not None:
+        _check(v_pool, "v_pool", q.dtype)
+    _check(out, "out")
+    if out.dtype not in (q.dtype, torch.float32):
+        raise KernelError(f"sink_attention: output {out.dtype} for queries {q.dtype}")
+    _check(tiles, "tiles", torch.int32)
+    _check(block_table, "block_table", torch.int32)
+    if sink is not None:
+        _check(sink, "sink", torch.float32)
+        if sink.numel() != heads:
+            raise KernelError(f"sink_attention: {sink.numel()} sinks for {heads} heads")
+    _check_pages(k_pool, v_pool, kv_heads, page, dim, vdim, "sink_attention")
+    if q.numel() < T * heads * dim or out.numel() < T * heads * vdim:
+        raise KernelError("sink_attention: q/out too small for the step")
+    if n_splits > 1:
+        _check(part_o, "part_o", torch.float32)
+        _check(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < T * heads * n_splits * vdim or part_ml.numel() < T * heads * n_splits * 2:
+            raise KernelError("sink_attention: split buffers too small")
+    lib = _lib("sink_attention")
+    _call(lib, lib.ember_sink_attention, _p(q), _p(k_pool), _p(v_pool), _p(out), c_int(dtype_code(q.dtype)),
+          c_int(1 if out.dtype == torch.float32 else 0), c_int(T), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), _p(tiles),
+          c_int(n_tiles), c_int(tile_q), _p(block_table), c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]),
+          c_int(window), c_int(keep_first), _p(sink), c_float(scale), c_int(n_splits), c_int(split_keys), _p(part_o), _p(part_ml),
+          _p(err), _stream(stream))
+
+
+# --------------------------------------------------------------------- routed feed-forward (csrc/moe.cu)
+MOE_TILE_ROWS = 32               # slots of one expert a block of the grouped products takes (its MOE_BM)
+MOE_MAX_EXPERTS, MOE_MAX_TOP = 256, 32
+
+
+def moe_max_tiles(n_pairs: int, experts: int) -> int:
+    """The most row tiles a step of ``n_pairs`` (token, choice) pairs can have: every expert may end in a ragged tile."""
+    return n_pairs // MOE_TILE_ROWS + experts
+
+
+def moe_route(logits: torch.Tensor, T: int, top: int, sel: torch.Tensor, wgt: torch.Tensor, stream: Optional[int] = None) -> None:
+    """sel[t] = the ``top`` experts with the largest logits (descending; ties: the lower index), wgt[t] = softmax over
+    those logits alone.  logits fp32 [T, experts]."""
+    _check(logits, "logits", torch.float32)
+    _check(sel, "sel", torch.int32)
+    _check(wgt, "wgt", torch.float32)
+    if logits.dim() != 2 or logits.shape[0] < T or sel.numel() < T * top or wgt.numel() < T * top:
+        raise KernelError("moe_route: buffers do not fit the step")
+    lib = _lib("moe")
+    _call(lib, lib.ember_moe_route, _p(logits), c_int(T), c_int(logits.shape[1]), c_int(top), _p(sel), _p(wgt), _stream(stream))
+
+
+def moe_group(sel: torch.Tensor, n_pairs: int, experts: int, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
+              slot_of_pair: torch.Tensor, tiles: torch.Tensor, stream: Optional[int] = None) -> int:
+    """Orders the (token, choice) pairs by expert.  offsets int32 [experts + 1]; pair_of_slot, slot_of_pair int32
+    [n_pairs]; tiles int32 [1 + 2 max_tiles]: the number of row tiles, then every tile's expert, then every tile's
+    first slot.  Returns max_tiles (what the products' grids are sized for)."""
+    for t, n in ((sel, "sel"), (offsets, "offsets"), (pair_of_slot, "pair_of_slot"), (slot_of_pair, "slot_of_pair"), (tiles, "tiles")):
+        _check(t, n, torch.int32)
+    mt = moe_max_tiles(n_pairs, experts)
+    if sel.numel() < n_pairs or offsets.numel() < experts + 1 or pair_of_slot.numel() < n_pairs or slot_of_pair.numel() < n_pairs or \
+            tiles.numel() < 1 + 2 * mt:
+        raise KernelError("moe_group: buffers do not fit the step")
+    lib = _lib("moe")
+    _call(lib, lib.ember_moe_group, _p(sel), c_int(n_pairs), c_int(experts), _p(offsets), _p(pair_of_slot), _p(slot_of_pair),
+          _off(tiles, 0), _off(tiles, 1), _off(tiles, 1 + mt), c_int(mt), _stream(stream))
+    return mt
+
+
+def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
+             tiles: torch.Tensor, max_tiles: int, top: int, gated: bool, limit: float = 0.0, alpha: float = 1.0,
+             stream: Optional[int] = None) -> None:
+    """The product of every slot's row with its expert's matrix (``w`` [experts, N, K]).  ``top`` > 0: a slot's row of
+    ``x`` is its token's (x [tokens, K], gathered through the pairs); 0: x has a row per slot.  ``gated``: w's rows are
+    interleaved (gate, up) and out[slot, j] = g sigmoid(alpha g) (u + 1) with g = min(gate, limit),
+    u = clamp(up, -limit, limit), in x's dtype; else out[slot] is the fp32 product."""
+    _check(x, "x")
+    _check(w, "w", x.dtype)
+    _check(out, "out", x.dtype if gated else torch.float32)
+    E, N, K = w.shape
+    n_out = N // 2 if gated else N
+    if x.shape[-1] != K or out.shape[-1] != n_out:
+        raise KernelError(f"moe_gemm: rows of {x.shape[-1]} -> {out.shape[-1]} against experts {tuple(w.shape)}")
+    lib = _lib("moe")
+    _call(lib, lib.ember_moe_gemm, _p(x), c_int(dtype_code(x.dtype)), c_int(K), _p(w), c_int(dtype_code(w.dtype)), c_longlong(N * K),
+          _p(out), c_int(dtype_code(out.dtype)), c_int(n_out), _p(offsets), _p(pair_of_slot), _off(tiles, 0), _off(tiles, 1),
+          _off(tiles, 1 + max_tiles), c_int(max_tiles), c_int(top), c_int(N), c_int(K), c_int(1 if gated else 0), c_float(limit),
+          c_float(alpha), _stream(stream))
+
+
+def moe_combine(y: torch.Tensor, wgt: torch.Tensor, slot_of_pair: torch.Tensor, T: int, top: int, out: torch.Tensor,
+                accumulate: bool = False, stream: Optional[int] = None) -> None:
+    """out[t] (+)= sum over the token's choices, in order, of wgt[t, k] * y[slot of (t, k)]; all fp32."""
+    _check(y, "y", torch.float32)
+    _check(wgt, "wgt", torch.float32)
+    _check(out, "out", torch.float32)
+    _check(slot_of_pair, "slot_of_pair", torch.int32)
+    hidden = out.shape[-1]
+    if y.shape[-1] != hidden or y.numel() < T * top * hidden or out.numel() < T * hidden:
+        raise KernelError("moe_combine: buffers do not fit the step")
+    lib = _lib("moe")
+    _call(lib, lib.ember_moe_combine, _p(y), _p(wgt), _p(slot_of_pair), c_int(T), c_int(top), _p(out), c_int(1 if accumulate else 0),
+          c_int(hidden), _stream(stream))

@@ -2,8 +2,8 @@
 from .base import CacheNeed, FeedForward, Gate, Mixer, Norm, Part, PositionEncoding, Runtime, WeightDecl
 from .registry import build_part, part_class, register_part, registered_parts
 from .linear import Linear
-from . import (norm, position, attention, feedforward, gate, recurrent, sigmoid_attention, parallel,  # noqa: F401
-               block)                                               # (registers the built-in parts)
+from . import (norm, position, attention, feedforward, gate, recurrent, sigmoid_attention, sink_attention,  # noqa: F401
+               parallel, block)                                               # (registers the built-in parts)
 
 __all__ = ["CacheNeed", "FeedForward", "Gate", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime", "WeightDecl",
            "build_part", "part_class", "register_part", "registered_parts", "Linear"]

@@ -50,7 +50,8 @@ class CacheNeed:
     """What a mixer asks of the cache manager, per layer.
 
     kind "full":   pages holding every key/value of the request.
-    kind "window": pages holding the last ``window`` keys; older pages are given back.
+    kind "window": pages holding the last ``window`` keys; older pages are given back, except those that hold one of
+                   the first ``keep_first`` keys (a window that keeps the sequence's first tokens in sight).
     kind "state":  no pages; one slot of ``state_shape`` elements of ``state_dtype`` per request.
     Layers whose needs are equal share a group (one block table, one page pool per group).
     """
@@ -60,6 +61,8 @@ class CacheNeed:
     head_dim: int = 0
     window: int = 0
     value_dim: int = 0            # size of a value head where it differs from a key head's (0: the same)
+    keep_first: int = 0           # kind "window": the first tokens of a request whose pages are never given back
+    keys_only: bool = False       # one row per token and head (a latent that serves as key and value): no value pool
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
 

@@ -16,6 +16,7 @@ from typing import Dict, List, Mapping, Optional
 
 import torch
 
+from .. import ops
 from ..config.spec import ConfigError
 from .base import CacheNeed, Runtime, WeightDecl
 from .registry import build_part, register_part
@@ -115,34 +116,61 @@ class GatedSandwichBlock(Arrangement):
 
     once for the mixer and once for the feed-forward (a layer may have no feed-forward, and either gate may be
     left out).  The sublayer stores its fp32 result in a buffer (``can_store``; others add into a zeroed one); gate,
-    output norm and the addition to the residual stream are one kernel (the output norm's ``gated_add``)."""
+    output norm and the addition to the residual stream are one kernel (the output norm's ``gated_add``).
+
+    The input norms may be left out as well: the sublayer then reads the residual stream itself,
+    ``h += norm_out(sublayer(h))``.  On the float32 path that is the stream's own buffer; on the bfloat16 path it is the
+    stream rounded once, which the ``gated_add`` before it leaves beside the new residual rows (the first sublayer of
+    a step, or one that follows another arrangement, rounds the stream in a kernel of its own)."""
 
     ROLES = {"mixer_norm": "norm", "mixer": "mixer", "mixer_gate": "gate", "mixer_out_norm": "norm",
              "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_gate": "gate",
              "feed_forward_out_norm": "norm"}
-    OPTIONAL = frozenset({"mixer_gate", "feed_forward_norm", "feed_forward", "feed_forward_gate", "feed_forward_out_norm"})
+    OPTIONAL = frozenset({"mixer_norm", "mixer_gate", "feed_forward_norm", "feed_forward", "feed_forward_gate",
+                          "feed_forward_out_norm"})
 
     def __init__(self, layer_spec):
         super().__init__(layer_spec)
         p = self.parts
-        if ("feed_forward" in p) != ("feed_forward_norm" in p) or ("feed_forward" in p) != ("feed_forward_out_norm" in p):
-            raise ConfigError("a gated-sandwich layer has a feed-forward with both of its norms, or none of the three")
+        if ("feed_forward" in p) != ("feed_forward_out_norm" in p) or ("feed_forward_norm" in p and "feed_forward" not in p):
+            raise ConfigError("a gated-sandwich layer has a feed-forward with its output norm (and maybe an input norm), or none")
         for role in ("mixer_out_norm", "feed_forward_out_norm"):
             if role in p and not hasattr(p[role], "gated_add"):
                 raise ConfigError(f"the norm in the role {role!r} cannot gate, norm and add in one kernel (no gated_add)")
 
+    def _stream(self, ctx, h):
+        """What a sublayer without an input norm reads: the stream itself (float32), or its bfloat16 rounding, made
+        here unless the kernel that last added to the stream left it (``ctx.memo`` says at which run of the schedule)."""
+        if self.rt.dtype == torch.float32:
+            return h, None
+        r = ctx.buf("block.stream_rounded", (ctx.max_tokens, h.shape[-1]), torch.bfloat16)
+        at = ctx.memo.get("schedule.index")
+        made = ctx.memo.get("block.stream_rounded.at")
+        if at is None or made is None or made not in (at, at - 1) or ctx.memo.get("block.stream_rounded.of") != h.data_ptr():
+            ops.round_rows(h, r, ctx.T * h.shape[-1], stream=ctx.stream)
+        return r, r
+
     def _sublayer(self, ctx, h, x, norm_in, run, gate, norm_out, can_store: bool) -> None:
         T, hidden = ctx.T, h.shape[-1]
         y = ctx.buf("block.sublayer", (ctx.max_tokens, hidden), torch.float32)
-        norm_in.forward(ctx, h, x, T)
+        rounded = None
+        if norm_in is not None:
+            norm_in.forward(ctx, h, x, T)
+        else:
+            x, rounded = self._stream(ctx, h)
         if not can_store:
             y[:T].zero_()
-        run(y)
+        run(x, y)
         logits = None
         if gate is not None:
             logits = ctx.buf("block.gate", (ctx.max_tokens, hidden), torch.float32)
             gate.forward(ctx, x, logits)
-        norm_out.gated_add(ctx, y, logits, h, T, gate_bias=getattr(gate, "bias", None))
+        if rounded is not None:
+            norm_out.gated_add(ctx, y, logits, h, T, gate_bias=getattr(gate, "bias", None), rounded=rounded)
+            ctx.memo["block.stream_rounded.at"] = ctx.memo.get("schedule.index")
+            ctx.memo["block.stream_rounded.of"] = h.data_ptr()
+        else:
+            norm_out.gated_add(ctx, y, logits, h, T, gate_bias=getattr(gate, "bias", None))
 
     def forward(self, ctx, h: torch.Tensor, caches, owns_cache: bool = True) -> None:
         p = self.parts
@@ -150,13 +178,13 @@ class GatedSandwichBlock(Arrangement):
         mixer = p["mixer"]
         store = bool(getattr(mixer, "can_store", False))
         kw = {"accumulate": False} if store else {}
-        self._sublayer(ctx, h, x, p["mixer_norm"], lambda y: mixer.forward(ctx, x, y, self.cache_of(caches), owns_cache, **kw),
+        self._sublayer(ctx, h, x, p.get("mixer_norm"), lambda x, y: mixer.forward(ctx, x, y, self.cache_of(caches), owns_cache, **kw),
                        p.get("mixer_gate"), p["mixer_out_norm"], store)
         ff = p.get("feed_forward")
         if ff is not None:
             store = bool(getattr(ff, "can_store", False))
             kw = {"accumulate": False} if store else {}
-            self._sublayer(ctx, h, x, p["feed_forward_norm"], lambda y: ff.forward(ctx, x, y, **kw),
+            self._sublayer(ctx, h, x, p.get("feed_forward_norm"), lambda x, y: ff.forward(ctx, x, y, **kw),
                            p.get("feed_forward_gate"), p["feed_forward_out_norm"], store)
 
 

@@ -54,4 +54,80 @@ class GatedMLP(FeedForward):
         self.down(ctx, act, residual, ctx.T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
 
 
+class RoutedMLP(FeedForward):
+    """Mixture of experts: h += sum over the token's ``top`` experts of weight * W_down (g sigmoid(alpha g) (u + 1)) with
+    g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit).  The router's logits W_router x are fp32 (fp32 weights
+    and accumulation); the chosen experts are the ``top`` largest (ties: the lower index) and their weights the softmax
+    over the chosen logits alone.
+
+    Device layout: every expert's gate and up rows interleaved into one [experts, 2 ff, hidden] tensor (the activation
+    is the first product's epilogue) and the down matrices as [experts, hidden, ff].  The step's (token, choice) pairs
+    are ordered by expert on the device; both products walk row tiles of one expert each, so every expert's weights
+    are read once per step however the tokens fall, and nothing comes back to the host (decode steps are captured
+    into CUDA graphs like any other).  Tensors under the prefix: router, e<i>.gate, e<i>.up, e<i>.down."""
+
+    graph_safe = True
+    can_store = True
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        s = spec
+        if min(s.hidden_size, s.intermediate_size, s.experts, s.top) <= 0 or s.top > s.experts:
+            raise ConfigError(f"routed feed-forward: top {s.top} of {s.experts} experts of {s.intermediate_size}")
+        if s.experts > ops.MOE_MAX_EXPERTS or s.top > ops.MOE_MAX_TOP:
+            raise ConfigError(f"routed feed-forward: at most {ops.MOE_MAX_TOP} of {ops.MOE_MAX_EXPERTS} experts")
+        if not s.limit > 0:
+            raise ConfigError("routed feed-forward: the clamp limit must be positive")
+
+    def weight_decls(self) -> List[WeightDecl]:
+        s, p = self.spec, self.prefix
+        d = [WeightDecl(p + "router", (s.experts, s.hidden_size))]
+        for e in range(s.experts):
+            d += [WeightDecl(f"{p}e{e}.gate", (s.intermediate_size, s.hidden_size)),
+                  WeightDecl(f"{p}e{e}.up", (s.intermediate_size, s.hidden_size)),
+                  WeightDecl(f"{p}e{e}.down", (s.hidden_size, s.intermediate_size))]
+        return d
+
+    def load(self, store, rt: Runtime) -> None:
+        s, p = self.spec, self.prefix
+        self.rt = rt
+        got = {d.name: store.take(d.name, d.shape) for d in self.weight_decls()}
+        if any(v is None for v in got.values()):
+            return
+        wd = rt.weight_dtype(got[f"{p}e0.gate"].dtype)
+        if wd != rt.dtype:
+            wd = torch.float32 if rt.dtype == torch.float32 else torch.bfloat16
+        self.router = Linear(rt.to_device(got[p + "router"], torch.float32))
+        gu = torch.empty((s.experts, s.intermediate_size, 2, s.hidden_size), dtype=wd, device=rt.device)
+        down = torch.empty((s.experts, s.hidden_size, s.intermediate_size), dtype=wd, device=rt.device)
+        for e in range(s.experts):
+            gu[e, :, 0] = rt.to_device(got[f"{p}e{e}.gate"], wd)
+            gu[e, :, 1] = rt.to_device(got[f"{p}e{e}.up"], wd)
+            down[e] = rt.to_device(got[f"{p}e{e}.down"], wd)
+        self.gate_up = gu.view(s.experts, 2 * s.intermediate_size, s.hidden_size)
+        self.down = down
+
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
+        s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
+        E, top, pairs = s.experts, s.top, ctx.T * s.top
+        if x.dtype != self.gate_up.dtype:
+            raise ops.KernelError(f"routed feed-forward: input {x.dtype} against experts {self.gate_up.dtype}")
+        logits = ctx.buf("routed_mlp.logits", (mt, E), torch.float32)
+        sel = ctx.buf("routed_mlp.sel", (mt * top,), torch.int32)
+        wgt = ctx.buf("routed_mlp.weights", (mt * top,), torch.float32)
+        offsets = ctx.buf("routed_mlp.offsets", (E + 1,), torch.int32)
+        pair_of_slot = ctx.buf("routed_mlp.pair_of_slot", (mt * top,), torch.int32)
+        slot_of_pair = ctx.buf("routed_mlp.slot_of_pair", (mt * top,), torch.int32)
+        tiles = ctx.buf("routed_mlp.tiles", (1 + 2 * ops.moe_max_tiles(mt * top, E),), torch.int32)
+        act = ctx.buf("routed_mlp.act", (mt * top, s.intermediate_size), rt.dtype)
+        y = ctx.buf("routed_mlp.down", (mt * top, s.hidden_size), torch.float32)
+        self.router(ctx, x, logits, T, ops.EPI_STORE_F32)
+        ops.moe_route(logits, T, top, sel, wgt, stream=ctx.stream)
+        max_tiles = ops.moe_group(sel, pairs, E, offsets, pair_of_slot, slot_of_pair, tiles, stream=ctx.stream)
+        ops.moe_gemm(x, self.gate_up, act, offsets, pair_of_slot, tiles, max_tiles, top, True, s.limit, s.alpha, stream=ctx.stream)
+        ops.moe_gemm(act, self.down, y, offsets, pair_of_slot, tiles, max_tiles, 0, False, stream=ctx.stream)
+        ops.moe_combine(y, wgt, slot_of_pair, T, top, residual, accumulate=accumulate, stream=ctx.stream)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "routed_mlp", RoutedMLP)

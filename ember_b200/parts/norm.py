@@ -17,11 +17,14 @@ from .registry import register_part
 class RMSNorm(Norm):
     graph_safe = True
 
+    def _name(self) -> str:
+        return self.prefix + getattr(self.spec, "weight_suffix", "weight")
+
     def weight_decls(self) -> List[WeightDecl]:
-        return [WeightDecl(self.prefix + "weight", (self.spec.size,), init="norm")]
+        return [WeightDecl(self._name(), (self.spec.size,), init="norm")]
 
     def load(self, store, rt: Runtime) -> None:
-        w = store.take(self.prefix + "weight", (self.spec.size,))
+        w = store.take(self._name(), (self.spec.size,))
         self.weight = rt.to_device(w, torch.float32) if w is not None else None
 
     def scale_output(self, scale: float) -> None:
@@ -32,10 +35,11 @@ class RMSNorm(Norm):
         ops.rmsnorm(x, self.weight, self.spec.eps, out, n_rows, rows=rows, stream=ctx.stream)
 
     def gated_add(self, ctx, y: torch.Tensor, gate_logits: Optional[torch.Tensor], residual: torch.Tensor, n_rows: int,
-                  gate_bias: Optional[torch.Tensor] = None) -> None:
-        """residual += norm(y * sigmoid(gate_logits + gate_bias)) in one kernel (no gate if ``gate_logits`` is None)."""
+                  gate_bias: Optional[torch.Tensor] = None, rounded: Optional[torch.Tensor] = None) -> None:
+        """residual += norm(y * sigmoid(gate_logits + gate_bias)) in one kernel (no gate if ``gate_logits`` is None);
+        ``rounded`` (bfloat16) also receives the new residual rows."""
         ops.gated_norm_add(y, gate_logits, self.weight, None, self.spec.eps, False, residual, n_rows, gate_bias=gate_bias,
-                           stream=ctx.stream)
+                           rounded=rounded, stream=ctx.stream)
 
 
 class LayerNorm(Norm):
@@ -63,10 +67,11 @@ class LayerNorm(Norm):
         ops.layer_norm(x, self.weight, self.bias, self.spec.eps, out, n_rows, rows=rows, stream=ctx.stream)
 
     def gated_add(self, ctx, y: torch.Tensor, gate_logits: Optional[torch.Tensor], residual: torch.Tensor, n_rows: int,
-                  gate_bias: Optional[torch.Tensor] = None) -> None:
-        """residual += norm(y * sigmoid(gate_logits + gate_bias)) in one kernel (no gate if ``gate_logits`` is None)."""
+                  gate_bias: Optional[torch.Tensor] = None, rounded: Optional[torch.Tensor] = None) -> None:
+        """residual += norm(y * sigmoid(gate_logits + gate_bias)) in one kernel (no gate if ``gate_logits`` is None);
+        ``rounded`` (bfloat16) also receives the new residual rows."""
         ops.gated_norm_add(y, gate_logits, self.weight, self.bias, self.spec.eps, True, residual, n_rows, gate_bias=gate_bias,
-                           stream=ctx.stream)
+                           rounded=rounded, stream=ctx.stream)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

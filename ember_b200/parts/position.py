@@ -40,7 +40,8 @@ class RotaryEmbedding(PositionEncoding):
         return self._table, self.spec.rotary_dim
 
     def table_key(self):
-        return (self.spec.rotary_dim, float(self.spec.theta), getattr(self.spec, "frequency_precision", "float32"))
+        return (self.spec.rotary_dim, float(self.spec.theta), getattr(self.spec, "frequency_precision", "float32"),
+                getattr(self.spec, "layout", "half"))
 
 
 class NoPosition(PositionEncoding):

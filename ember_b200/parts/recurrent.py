@@ -2,9 +2,10 @@
 
 * "channel_delta": delta-rule memory with a decay per head and key channel,
 * "mlstm":         matrix memory with an exponential input gate and a running maximum,
-* "mamba2":        selective state space with a scalar decay per head.
+* "mamba2":        selective state space with a scalar decay per head,
+* "gla":           linear attention with a decay per head and key channel (no convolution, no delta correction).
 
-All three project their input with one fused product whose fp32 result the recurrence kernel reads in place (column
+All of them project their input with one fused product whose fp32 result the recurrence kernel reads in place (column
 offsets, no copies), run the same kernels for prompt portions and single tokens (a block walks its run's tokens in
 order, so the state after a step does not depend on how the tokens were cut), normalise each head's read-out in
 fp32 and end in an output product that stores into, or adds into, an fp32 [T, hidden] buffer.  A short causal
@@ -249,6 +250,75 @@ class StateSpace(_StateMixer):
         self._out(ctx, y, out, accumulate)
 
 
+# ------------------------------------------------------------------------------------------------- gla
+class GatedLinearAttention(_StateMixer):
+    """Per head, with q = W_q x * dim^-1/2, k = W_k x, v = W_v x and one decay per key channel
+    alpha = sigmoid(W_a2 (W_a1 x) + b)^(1 / tau) (computed as exp(logsigmoid(.) / tau) in fp32):
+
+        S <- diag(alpha) S + k v^T;  o = S^T q
+
+    then o / rms(o) per head times norm (size vdim, shared by the heads), times silu(W_g x), and the output product.
+    The state starts at zero and is carried in the request's slot.  Tensors under the prefix: q, k, v, g, o, norm, a1,
+    a2, a2.b."""
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        s = spec
+        if min(s.num_heads, s.head_dim, s.value_dim) <= 0 or not s.tau > 0:
+            raise ConfigError("gla: head count, sizes and tau must be positive")
+        self.qk, self.vd = s.num_heads * s.head_dim, s.num_heads * s.value_dim
+        self.decay_rank = s.decay_rank
+
+    def state_floats(self) -> int:
+        s = self.spec
+        return s.num_heads * s.head_dim * s.value_dim
+
+    def weight_decls(self) -> List[WeightDecl]:
+        s, p = self.spec, self.prefix
+        hid, ra = s.hidden_size, self.decay_rank
+        if ra <= 0:
+            raise ConfigError("gla: the rank of the decay projection is read from the weights at load; a configuration "
+                              "that lists tensors without a file must give it")
+        return [WeightDecl(p + "q", (self.qk, hid)), WeightDecl(p + "k", (self.qk, hid)), WeightDecl(p + "v", (self.vd, hid)),
+                WeightDecl(p + "g", (self.vd, hid)), WeightDecl(p + "o", (hid, self.vd)),
+                WeightDecl(p + "norm", (s.value_dim,), init="norm"),
+                WeightDecl(p + "a1", (ra, hid)), WeightDecl(p + "a2", (self.qk, ra)),
+                WeightDecl(p + "a2.b", (self.qk,), init="uniform", lo=0.0, hi=4.0)]
+
+    def load(self, store, rt: Runtime) -> None:
+        p = self.prefix
+        self.rt = rt
+        if self.decay_rank <= 0:                       # a size the configuration leaves to the weights
+            shape = store.shape(p + "a1")
+            self.decay_rank = int(shape[0]) if shape and len(shape) == 2 else 1
+        w = self._take_all(store)
+        if w is None:
+            return
+        self.in_proj = self._fused([w[p + n] for n in ("q", "k", "v", "g")], rt)
+        self.low = Linear.from_host(w[p + "a1"], rt)
+        self.up = Linear.from_host(w[p + "a2"], rt)
+        self.o = Linear.from_host(w[p + "o"], rt)
+        self.decay_bias, self.norm_w = (rt.to_device(w[p + n], torch.float32) for n in ("a2.b", "norm"))
+
+    def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
+        s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
+        H, D, V = s.num_heads, s.head_dim, s.value_dim
+        off_k, off_v, off_g = self.qk, 2 * self.qk, 2 * self.qk + self.vd
+        proj = ctx.buf("gla.proj", (mt, off_g + self.vd), torch.float32)
+        low = ctx.buf("gla.low", (mt, self.decay_rank), rt.dtype)
+        z = ctx.buf("gla.decay", (mt, self.qk), torch.float32)
+        o = ctx.buf("gla.read", (mt, self.vd), torch.float32)
+        y = ctx.buf("gla.normed", (mt, self.vd), rt.dtype)
+        self.in_proj(ctx, x, proj, T, ops.EPI_STORE_F32)
+        self.low(ctx, x, low, T, ops.EPI_STORE)
+        self.up(ctx, low, z, T, ops.EPI_STORE_F32)
+        ops.gla_scan(proj, 0, off_k, off_v, z, 0, self.decay_bias, 1.0 / s.tau, cache.state, o, ctx.query_start, ctx.state_slots,
+                     T, ctx.S, H, D, V, stream=ctx.stream)
+        ops.group_norm_gate(o, 0, proj, off_g, self.norm_w, False, s.norm_eps, ops.GATE_SILU_AFTER, y, T, H, V, stream=ctx.stream)
+        self._out(ctx, y, out, accumulate)
+
+
+register_part("mixer", "gla", GatedLinearAttention)
 register_part("mixer", "channel_delta", GatedDelta)
 register_part("mixer", "mlstm", MatrixMemory)
 register_part("mixer", "mamba2", StateSpace)

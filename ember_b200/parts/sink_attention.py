@@ -1,0 +1,212 @@
+"""Softmax attention whose denominator also holds a learned sink per head, in two mixers:
+
+* "sink_attention": grouped-query attention with optional biases on q, k, v, an optional RMS norm over the *whole*
+  query projection and over the whole key projection (all heads at once, before the split into heads), no rotation,
+  keys of ``head_dim`` and values of ``value_dim``, and a window that keeps the first tokens in sight: position i sees
+  j <= i with i - j < window or j < keep_first.  Its cache group is of kind "window" with ``keep_first``: pages the
+  window has passed go back while the request runs, those of the kept first tokens stay.
+* "latent_attention": queries through a low-rank latent (c_q = RMSNorm(W_dq h), q = W_uq c_q, per head
+  [head_dim unrotated | rot_dim rotated]); W_dkv h = [kv_rank | rot_dim] gives the RMS-normed latent c and a rotated
+  key part shared by the heads; a head's unrotated key is W_uk c and its value W_uv c.  Only [c | rotated part] is
+  cached, one row per token (``keys_only``).  The up-projections never touch the cache: with
+  q~_h = W_uk[h]^T q_h the score is (q~_h . c + q_rot . k_rot) * scale, and the head's output is W_uv[h] applied to the
+  attended latent sum_j w_j c_j, so the attention runs over the cache rows themselves with every query head sharing the
+  one row (keys [c | k_rot], values its first kv_rank elements) and the two per-head products are small batched
+  products around it.  The concatenated heads are multiplied by sigmoid(W_g h) in the second product's epilogue.
+  A layer without W_dkv (``own_kv`` False) reads another layer's cache rows as that layer left them.
+
+The sink has no key and no value: it adds exp(sink[h]) to the softmax's denominator once, unscaled.  Scores, weights,
+norms, angles and sums are fp32 in both dtypes.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .. import ops
+from ..config.spec import ConfigError
+from .base import CacheNeed, Mixer, Runtime, WeightDecl
+from .linear import Linear
+from .registry import build_part, register_part
+
+
+class _SinkSoftmax(Mixer):
+    """What the two mixers share: cutting long key ranges of small steps into splits, and the attention call."""
+
+    graph_safe = True
+    can_store = True
+
+    SPLIT_KEYS = 256            # keys per split, and the most tokens in a step for which key ranges are split
+    SPLIT_MAX_TOKENS = 64
+
+    def _attend(self, ctx, q, k_pool, v_pool, out, table, page, heads, kv_heads, dim, vdim, window, keep_first, sink, scale):
+        tile_q = ops.sink_attention_tile_queries(heads // kv_heads)
+        tiles, n_tiles = ctx.attention_tiles(tile_q, "all")
+        span = ctx.max_context if window <= 0 else min(ctx.max_context, window + keep_first + tile_q)
+        n_splits, part_o, part_ml = 1, None, None
+        if ctx.T <= self.SPLIT_MAX_TOKENS and span > 2 * self.SPLIT_KEYS:
+            n_splits = (ctx.max_context + self.SPLIT_KEYS - 1) // self.SPLIT_KEYS
+            part_o = ctx.buf_dyn("sink_attention.part_o", ctx.T * heads * n_splits * vdim, torch.float32)
+            part_ml = ctx.buf_dyn("sink_attention.part_ml", ctx.T * heads * n_splits * 2, torch.float32)
+        ops.sink_attention(q, k_pool, v_pool, out, ctx.T, heads, kv_heads, dim, vdim, tiles, n_tiles, tile_q, table, page,
+                           window, keep_first, sink, scale, n_splits, self.SPLIT_KEYS, part_o, part_ml, err=ctx.err,
+                           stream=ctx.stream)
+
+
+class SinkAttention(_SinkSoftmax):
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        s = spec
+        if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
+            raise ConfigError(f"{s.num_heads} heads do not divide into {s.num_kv_heads} key/value heads")
+        if s.head_dim <= 0 or not 0 < s.value_dim <= 512:
+            raise ConfigError(f"sink attention: heads of {s.head_dim} / {s.value_dim} (values up to 512)")
+        if s.qk_norm not in ("none", "whole"):
+            raise ConfigError(f"sink attention: qk_norm {s.qk_norm!r} (none, whole)")
+        if s.window < 0 or s.keep_first < 0:
+            raise ConfigError("sink attention: window and keep_first must be >= 0")
+        self.q_dim, self.k_dim, self.v_dim = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim, s.num_kv_heads * s.value_dim
+
+    def weight_decls(self) -> List[WeightDecl]:
+        s, p = self.spec, self.prefix
+        d = [WeightDecl(p + "q", (self.q_dim, s.hidden_size)), WeightDecl(p + "k", (self.k_dim, s.hidden_size)),
+             WeightDecl(p + "v", (self.v_dim, s.hidden_size)), WeightDecl(p + "o", (s.hidden_size, s.num_heads * s.value_dim))]
+        if s.bias:
+            d += [WeightDecl(p + "q.b", (self.q_dim,), init="zeros"), WeightDecl(p + "k.b", (self.k_dim,), init="zeros"),
+                  WeightDecl(p + "v.b", (self.v_dim,), init="zeros")]
+        if s.qk_norm == "whole":
+            d += [WeightDecl(p + "q.norm", (self.q_dim,), init="norm"), WeightDecl(p + "k.norm", (self.k_dim,), init="norm")]
+        if s.sink:
+            d.append(WeightDecl(p + "sink", (s.num_heads,), init="uniform", lo=-1.0, hi=1.0))
+        return d
+
+    def load(self, store, rt: Runtime) -> None:
+        s, p = self.spec, self.prefix
+        self.rt = rt
+        got = {d.name: store.take(d.name, d.shape) for d in self.weight_decls()}
+        if any(v is None for v in got.values()):
+            return
+        wd = rt.weight_dtype(got[p + "q"].dtype)
+        self.qkv = Linear(torch.cat([rt.to_device(got[p + n], wd) for n in "qkv"], dim=0).contiguous())
+        self.o = Linear.from_host(got[p + "o"], rt)
+        f32 = lambda name: rt.to_device(got[p + name], torch.float32)          # noqa: E731
+        self.bias = torch.cat([f32(n + ".b") for n in "qkv"]).contiguous() if s.bias else None
+        self.q_norm_w = f32("q.norm") if s.qk_norm == "whole" else None
+        self.k_norm_w = f32("k.norm") if s.qk_norm == "whole" else None
+        self.sink = f32("sink") if s.sink else None
+
+    def cache_need(self) -> CacheNeed:
+        s = self.spec
+        return CacheNeed(kind="window" if s.window > 0 else "full", num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
+                         window=s.window, value_dim=s.value_dim if s.value_dim != s.head_dim else 0,
+                         keep_first=s.keep_first if s.window > 0 else 0)
+
+    def tile_requests(self):
+        return [(ops.sink_attention_tile_queries(self.spec.num_heads // self.spec.num_kv_heads), "all")]
+
+    def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
+        s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
+        H, G, D, V = s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim
+        qkv = ctx.buf("sink_attention.qkv", (mt, self.q_dim + self.k_dim + self.v_dim), torch.float32)
+        q = ctx.buf("sink_attention.q", (mt, self.q_dim), rt.dtype)
+        att = ctx.buf("sink_attention.out", (mt, H * V), rt.dtype)
+        table = ctx.block_table(cache.group)
+        self.qkv(ctx, x, qkv, T, ops.EPI_STORE_F32)
+        ops.whole_norm_store(qkv, self.bias, self.q_norm_w, self.k_norm_w, s.qk_norm_eps, T, H, G, D, V, ctx.positions,
+                             ctx.seq_of, table, cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
+                             stream=ctx.stream)
+        self._attend(ctx, q, cache.k, cache.v, att, table, cache.page_tokens, H, G, D, V, s.window, s.keep_first, self.sink,
+                     s.scale)
+        self.o(ctx, att, out, T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
+
+
+class LatentAttention(_SinkSoftmax):
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        s = spec
+        if min(s.num_heads, s.head_dim, s.value_dim, s.q_rank, s.kv_rank) <= 0 or s.rot_dim < 0:
+            raise ConfigError("latent attention: head count, sizes and ranks must be positive")
+        if s.kv_rank > 512:
+            raise ConfigError(f"latent attention: a latent of {s.kv_rank} (up to 512)")
+        self.position = build_part("position", s.position)
+        rotary = getattr(s.position, "rotary_dim", 0)
+        if rotary and (getattr(s.position, "layout", "half") != "interleaved" or rotary > s.rot_dim):
+            raise ConfigError("latent attention rotates neighbouring pairs of the rotated part (layout 'interleaved', "
+                              f"at most rot_dim = {s.rot_dim} elements)")
+        self.q_head = s.head_dim + s.rot_dim          # a query head as W_uq makes it
+        self.row = s.kv_rank + s.rot_dim              # a cache row, and a query head as the attention reads it
+
+    def weight_decls(self) -> List[WeightDecl]:
+        s, p = self.spec, self.prefix
+        H, hid = s.num_heads, s.hidden_size
+        d = [WeightDecl(p + "dq", (s.q_rank, hid)), WeightDecl(p + "dq.norm", (s.q_rank,), init="norm"),
+             WeightDecl(p + "uq", (H * self.q_head, s.q_rank))]
+        if s.own_kv:
+            d += [WeightDecl(p + "dkv", (self.row, hid)), WeightDecl(p + "dkv.norm", (s.kv_rank,), init="norm")]
+        d += [WeightDecl(p + "uk", (H * s.head_dim, s.kv_rank)), WeightDecl(p + "uv", (H * s.value_dim, s.kv_rank))]
+        if s.sink:
+            d.append(WeightDecl(p + "sink", (H,), init="uniform", lo=-1.0, hi=1.0))
+        if s.gate:
+            d.append(WeightDecl(p + "g", (H * s.value_dim, hid)))
+        d.append(WeightDecl(p + "o", (hid, H * s.value_dim)))
+        return d
+
+    def load(self, store, rt: Runtime) -> None:
+        s, p = self.spec, self.prefix
+        self.rt = rt
+        got = {d.name: store.take(d.name, d.shape) for d in self.weight_decls()}
+        if any(v is None for v in got.values()):
+            return
+        wd = rt.weight_dtype(got[p + "dq"].dtype)
+        H = s.num_heads
+        # one product for everything that reads the layer's input: [query latent | key/value latent, key part | gate]
+        fused = [got[p + "dq"]] + ([got[p + "dkv"]] if s.own_kv else []) + ([got[p + "g"]] if s.gate else [])
+        self.down = Linear(torch.cat([rt.to_device(t, wd) for t in fused], dim=0).contiguous())
+        self.c_col = s.q_rank
+        self.g_col = s.q_rank + (self.row if s.own_kv else 0)
+        self.uq = Linear.from_host(got[p + "uq"], rt)
+        # per head: [kv_rank, head_dim] (the key up-projection transposed: it multiplies the query) and [value_dim, kv_rank]
+        self.uk_t = rt.to_device(got[p + "uk"], wd).view(H, s.head_dim, s.kv_rank).transpose(1, 2).contiguous()
+        self.uv = rt.to_device(got[p + "uv"], wd).view(H, s.value_dim, s.kv_rank).contiguous()
+        self.o = Linear.from_host(got[p + "o"], rt)
+        f32 = lambda name: rt.to_device(got[p + name], torch.float32)          # noqa: E731
+        self.dq_norm_w = f32("dq.norm")
+        self.dkv_norm_w = f32("dkv.norm") if s.own_kv else None
+        self.sink = f32("sink") if s.sink else None
+        self.inv_freq, self.rotary = self.position.rotary_table(rt)
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kind="full", num_kv_heads=1, head_dim=self.row, keys_only=True)
+
+    def tile_requests(self):
+        return [(ops.sink_attention_tile_queries(self.spec.num_heads), "all")]
+
+    def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
+        s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
+        H, D, R, V, r = s.num_heads, s.head_dim, s.rot_dim, s.value_dim, s.kv_rank
+        a = ctx.buf("latent_attention.down", (mt, self.down.n), torch.float32)
+        cq = ctx.buf("latent_attention.cq", (mt, s.q_rank), rt.dtype)
+        qf = ctx.buf("latent_attention.q", (mt, H * self.q_head), torch.float32)
+        q = ctx.buf("latent_attention.q_latent", (mt, H * self.row), rt.dtype)
+        lat = ctx.buf("latent_attention.attended", (mt, H * r), torch.float32)
+        og = ctx.buf("latent_attention.out", (mt, H * V), rt.dtype)
+        table = ctx.block_table(cache.group)
+        write = bool(owns_cache and s.own_kv)
+        self.down(ctx, x, a, T, ops.EPI_STORE_F32)
+        ops.latent_prepare(a, 0, s.q_rank, self.c_col, r, R, self.dq_norm_w, self.dkv_norm_w, s.norm_eps, self.inv_freq,
+                           self.rotary, T, ctx.positions, ctx.seq_of, table, cache.page_tokens, cq, cache.k if write else None,
+                           write_kv=write, err=ctx.err, stream=ctx.stream)
+        self.uq(ctx, cq, qf, T, ops.EPI_STORE_F32)
+        # a query head as the attention reads it: [W_uk[h]^T q_unrotated | q_rotated]
+        ops.head_gemm(qf, self.q_head, 0, self.uk_t, q, self.row, 0, T, stream=ctx.stream)
+        if R:
+            ops.rotate_pairs(qf, self.q_head, D, q, self.row, r, T, H, R, self.rotary, self.inv_freq, ctx.positions,
+                             stream=ctx.stream)
+        self._attend(ctx, q, cache.k, None, lat, table, cache.page_tokens, H, 1, self.row, r, 0, 0, self.sink, s.scale)
+        ops.head_gemm(lat, r, 0, self.uv, og, V, 0, T, gate=a if s.gate else None, gate_col=self.g_col, stream=ctx.stream)
+        self.o(ctx, og, out, T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
+
+
+register_part("mixer", "sink_attention", SinkAttention)
+register_part("mixer", "latent_attention", LatentAttention)

@@ -89,6 +89,7 @@ def library() -> ctypes.CDLL:
             "ember_cache_admit": (c_int, [c_void_p]), "ember_cache_slot": (c_int, [c_void_p, c_int]),
             "ember_cache_tokens": (ctypes.c_longlong, [c_void_p, c_int]),
             "ember_cache_first_live": (c_int, [c_void_p, c_int, c_int]),
+            "ember_cache_set_keep": (c_int, [c_void_p, c_int, c_int]),
             "ember_cache_table": (c_int, [c_void_p, c_int, c_int, POINTER(i32p)]),
             "ember_cache_ensure": (c_int, [c_void_p, c_int, ctypes.c_longlong]),
             "ember_cache_advance": (c_int, [c_void_p, c_int, ctypes.c_longlong]),

@@ -6,7 +6,8 @@
 //
 // Pages: ids 0..n-1; a fresh pool hands out low ids first, afterwards the most recently freed page first.
 // Groups: kind 0 keeps all keys, kind 1 a window of them (pages wholly older than the window go back as soon
-// as no later query can see them), kind 2 is fixed-size state (no pages).  Every admitted request holds one
+// as no later query can see them; pages that hold one of the first `keep` keys never do), kind 2 is fixed-size
+// state (no pages).  Every admitted request holds one
 // slot and one block table per group (-1 = page given back).
 #include <cstdint>
 #include <cstdio>
@@ -59,7 +60,7 @@ struct Pool {
 };
 
 struct Group {
-    int kind = 0, window = 0;
+    int kind = 0, window = 0, keep = 0;
     Pool pool;
     bool paged() const { return kind != 2; }
 };
@@ -134,6 +135,14 @@ void* ember_cache_create(int n_groups, const int32_t* kinds, const int32_t* wind
     return c;
 }
 void ember_cache_destroy(void* c) { delete (Core*)c; }
+
+// The first `keep` keys of every request stay in sight of a window group: their pages are never given back early.
+int ember_cache_set_keep(void* cv, int g, int keep) {
+    Core* c = (Core*)cv;
+    if (g < 0 || g >= (int)c->groups.size() || keep < 0) return -1;
+    c->groups[g].keep = keep;
+    return 0;
+}
 
 // The pool of group g (for the queries above); null for a state group.
 void* ember_cache_pool(void* cv, int g) {
@@ -210,7 +219,8 @@ int ember_cache_advance(void* cv, int h, long long tokens) {
         const long long dead = first_key / c->page;
         auto& t = r->tables[g];
         const long long stop = dead < (long long)t.size() ? dead : (long long)t.size();
-        for (long long i = r->first_live[g]; i < stop; i++) {
+        const long long kept = ((long long)grp.keep + c->page - 1) / c->page;      // pages of the kept first keys
+        for (long long i = r->first_live[g] > kept ? r->first_live[g] : kept; i < stop; i++) {
             if (t[i] >= 0) {
                 grp.pool.release(t[i]);
                 t[i] = -1;
