@@ -145,3 +145,12 @@ def test_plain_router_and_expert():
     out = routed_experts(h, W, "r.", mlp)
     want = wgt[0, 0] * clamped_expert(h, W, "r.e0.", 2.0) + wgt[0, 1] * clamped_expert(h, W, "r.e2.", 2.0)
     assert torch.allclose(out, want)
+
+
+def test_cli_info_and_random(tmp_path, capsys):
+    """`python -m ember_b200 info` on a folder written by the random-weights mode."""
+    from ember_b200 import cli
+    d = write_zufusun_dir("u", str(tmp_path / "m"), drop_ranks=False)
+    assert cli.main(["info", "-m", d]) in (0, None)
+    out = capsys.readouterr().out
+    assert "zufusun: 5 layers" in out and "state per request" in out
