@@ -19,6 +19,7 @@ Other workloads of the same engine, one JSON line each (not part of the default 
     python bench.py --workload serving-8b    # Qwen3-8B shape: 64 requests, prompts U[128, 2048], 512-token portions, 256 tokens each
     python bench.py --workload qwen3-32b     # Qwen3-32B shape: 2,048-token prefill, decode at batch 1 and 8 to 4,096, cache from free memory
     python bench.py --workload fadosun [--breakdown]   # Fadosun beside Qwen3 at equal width, feed-forward and layers
+    python bench.py --workload zufusun [--breakdown]   # Zufusun (two of eight experts a token) beside Qwen3 likewise
 """
 from __future__ import annotations
 
@@ -337,22 +338,61 @@ FADOSUN_LAYERS = [
 ]
 
 
+ZUFUSUN_LAYERS = [
+    {"type": "gla", "mixer": {"heads": 16, "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64}},
+    {"type": "attention", "mixer": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 0.0884,
+                                    "mask": {"size": 512, "keep_first": 4}}},
+    {"type": "latent_attention", "mixer": {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 768, "kv_rank": 512,
+                                           "scale": 0.0722, "rot": {"dims": 64, "base": 1e6}}},
+    {"type": "latent_attention", "mixer": {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 768, "kv_rank": 512,
+                                           "scale": 0.0722, "rot": {"dims": 64, "base": 1e6}, "kv_from": -1}},
+]
+
+
 def workload_fadosun(args, pk) -> int:
     """Fadosun beside Qwen3 at equal width, feed-forward, vocabulary and number of layers (the 1.7B widths, 8 layers
     unless --layers says otherwise; random weights): prefill of 512 and 2,048 tokens and decode steps at batch 8 and 64
     from a context of 1,024; with --breakdown instead the device time per kernel of one 2,048-token prefill and of a
     decode step at batch 64 (kernels serialised: no programmatic dependent launch, no graphs)."""
+    from ember_b200.config import FadosunConfig
+    n_layers = args.layers or 8
+    width, ff, vocab = QWEN3_1P7B["hidden_size"], QWEN3_1P7B["intermediate_size"], QWEN3_1P7B["vocab_size"]
+    fcfg = FadosunConfig.from_json({"architecture": "Fadosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+                                    "layers": [dict(FADOSUN_LAYERS[i % 4], mlp={"kind": "dense", "ff": ff}) for i in range(n_layers)]})
+    return beside_qwen3(args, pk, "fadosun", fcfg, n_layers, {"fadosun_layers": [l["type"] for l in FADOSUN_LAYERS]})
+
+
+def workload_zufusun(args, pk) -> int:
+    """Zufusun beside Qwen3 at equal width, vocabulary and number of layers (the 1.7B widths, 8 layers unless --layers
+    says otherwise; random weights), its feed-forward eight experts of half Qwen3's feed-forward size of which a token
+    uses two (the same products per token, four times the weights): the measurements of ``--workload fadosun``."""
+    from ember_b200.config import ZufusunConfig
+    n_layers = args.layers or 8
+    width, ff, vocab = QWEN3_1P7B["hidden_size"], QWEN3_1P7B["intermediate_size"], QWEN3_1P7B["vocab_size"]
+    mlp = {"kind": "moe", "expert": {"ff": ff // 2, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+    layers = []
+    for i in range(n_layers):
+        l = json.loads(json.dumps(ZUFUSUN_LAYERS[i % 4]))
+        if l["mixer"].get("kv_from") == -1:
+            l["mixer"]["kv_from"] = i - 1              # the latent of the layer before it
+        layers.append(dict(l, mlp=mlp))
+    zcfg = ZufusunConfig.from_json({"architecture": "Zufusun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers})
+    return beside_qwen3(args, pk, "zufusun", zcfg, n_layers, {"zufusun_layers": [l["type"] for l in ZUFUSUN_LAYERS],
+                                                             "experts": 8, "top": 2, "expert_ff": ff // 2})
+
+
+def beside_qwen3(args, pk, label, fcfg, n_layers, extra) -> int:
+    """A design (``fcfg``) and Qwen3 at the 1.7B widths and ``n_layers`` layers, one after the other: prefill of 512 and
+    2,048 tokens and decode steps at batch 8 and 64 from a context of 1,024, or with --breakdown the device time per
+    kernel of one 2,048-token prefill and of a decode step at batch 64."""
     import torch
     import ember_b200
     from ember_b200 import ops
-    from ember_b200.config import FadosunConfig, Qwen3Config
+    from ember_b200.config import Qwen3Config
     if args.breakdown:
         os.environ["EMBER_PDL"] = "0"          # kernels one after the other: each one's own time
-    n_layers = args.layers or 8
     width, ff, vocab = QWEN3_1P7B["hidden_size"], QWEN3_1P7B["intermediate_size"], QWEN3_1P7B["vocab_size"]
     context, warmup = 1024, max(3, args.warmup)
-    fcfg = FadosunConfig.from_json({"architecture": "Fadosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-                                    "layers": [dict(FADOSUN_LAYERS[i % 4], mlp={"kind": "dense", "ff": ff}) for i in range(n_layers)]})
     qcfg = Qwen3Config.from_json(dict(QWEN3_1P7B, num_hidden_layers=n_layers))
 
     def build(cfg, batch):
@@ -409,11 +449,12 @@ def workload_fadosun(args, pk) -> int:
             r.release(rid)
         return out
 
-    result = {"workload": "fadosun", "layers": n_layers, "width": width, "ff": ff, "vocab": vocab, "dtype": "bf16",
+    result = {"workload": label, "layers": n_layers, "width": width, "ff": ff, "vocab": vocab, "dtype": "bf16",
               "data": "synthetic (random weights from a seed, random token ids)", "decode_from": context,
-              "page_tokens": PAGE_TOKENS, "fadosun_layers": [l["type"] for l in FADOSUN_LAYERS], "peaks": pk["source"]}
+              "page_tokens": PAGE_TOKENS, "peaks": pk["source"]}
+    result.update(extra)
     with ClockSampler() as clocks:
-        for name, cfg in (("fadosun", fcfg), ("qwen3", qcfg)):
+        for name, cfg in ((label, fcfg), ("qwen3", qcfg)):
             res = {}
             llm = build(cfg, 64)
             if args.breakdown:
@@ -581,7 +622,7 @@ def main() -> int:
                     help="profiling aid: device time per kernel of three decode steps and one 2,048-token prefill step "
                          "(kernels serialised: EMBER_PDL=0 and no CUDA graphs are set by this flag)")
     ap.add_argument("--page-tokens", type=int, default=PAGE_TOKENS, choices=[16, 32, 64], help="tokens per cache page")
-    ap.add_argument("--workload", default="default", choices=["default", "serving-8b", "qwen3-32b", "fadosun"],
+    ap.add_argument("--workload", default="default", choices=["default", "serving-8b", "qwen3-32b", "fadosun", "zufusun"],
                     help="default: the Qwen3-1.7B line; serving-8b and qwen3-32b are BASELINE's fourth "
                          "and fifth configurations; fadosun: that design beside Qwen3 at equal sizes (with --breakdown "
                          "also per kernel); one JSON line each")
@@ -627,6 +668,8 @@ def main() -> int:
         return workload_qwen3_32b(args, pk)
     if args.workload == "fadosun":
         return workload_fadosun(args, pk)
+    if args.workload == "zufusun":
+        return workload_zufusun(args, pk)
     if args.breakdown:
         return breakdown(cfg, n_layers, args.batch)
     if args.only_prefill:

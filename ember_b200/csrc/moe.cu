@@ -189,6 +189,29 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(MoeGemmArgs p) {
     }
 }
 
+// xs[slot] = x[token of the slot's pair]: the rows of each expert side by side, for products that want plain matrices.
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ pair_of_slot, int top, uint4* __restrict__ xs,
+                                  int row16) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int slot = blockIdx.x;
+    const uint4* src = x + (size_t)(pair_of_slot[slot] / top) * row16;
+    uint4* dst = xs + (size_t)slot * row16;
+    for (int i = threadIdx.x; i < row16; i += blockDim.x) dst[i] = src[i];
+}
+
+// act[slot, j] = g sigmoid(alpha g) (u + 1), g = min(gu[slot, 2j], limit), u = clamp(gu[slot, 2j + 1], -limit, limit).
+template <typename TO>
+__global__ void moe_activation_kernel(const float2* __restrict__ gu, TO* __restrict__ act, size_t n, float limit, float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float2 v = gu[i];
+    const float g = fminf(v.x, limit), u = fminf(fmaxf(v.y, -limit), limit);
+    act[i] = from_float<TO>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wgt, const int* __restrict__ slot_of_pair,
                                    int top, float* __restrict__ out, int accumulate, int hidden) {
     pdl_launch_dependents();
@@ -245,6 +268,24 @@ EMBER_API int ember_moe_gemm(const void* x, int x_dtype, int ld_x, const void* w
         else return fail("moe_gemm: unsupported dtypes %d", key);
     }
     return check_launch("moe_gemm");
+}
+
+EMBER_API int ember_moe_gather(const void* x, const int* pair_of_slot, int n_pairs, int top, void* xs, int row_bytes, void* stream) {
+    if (n_pairs <= 0) return 0;
+    if (row_bytes <= 0 || row_bytes % 16) return fail("moe_gather: rows of %d bytes (a multiple of 16)", row_bytes);
+    launch_kernel(moe_gather_kernel, n_pairs, 128, 0, (cudaStream_t)stream, (const uint4*)x, pair_of_slot, top, (uint4*)xs, row_bytes / 16);
+    return check_launch("moe_gather");
+}
+
+EMBER_API int ember_moe_activation(const float* gu, void* act, int out_dtype, long long n, float limit, float alpha, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_dtype == EMBER_F32) launch_kernel(moe_activation_kernel<float>, blocks, 256, 0, st, (const float2*)gu, (float*)act, (size_t)n, limit, alpha);
+    else if (out_dtype == EMBER_BF16)
+        launch_kernel(moe_activation_kernel<__nv_bfloat16>, blocks, 256, 0, st, (const float2*)gu, (__nv_bfloat16*)act, (size_t)n, limit, alpha);
+    else return fail("moe_activation: unsupported dtype %d", out_dtype);
+    return check_launch("moe_activation");
 }
 
 EMBER_API int ember_moe_combine(const float* y, const float* wgt, const int* slot_of_pair, int T, int top, float* out, int accumulate,

@@ -314,69 +314,100 @@ sink_attention_kernel(SinkAttnParams p) {
     }
 
     const int* bt = p.block_table + (size_t)seq * p.max_blocks;
+    const bool vec4 = (D & 3) == 0;                       // (query rows are read four elements at a time then)
     for (int part = 0; part < 2; part++) {
         const int a = max(part == 0 ? 0 : lo, s_lo), b = min(part == 0 ? kept : hi, s_hi);
         if (a >= b) continue;
         for (int k0 = a - (a % SA_KT); k0 < b; k0 += SA_KT) {
             __syncthreads();  // the previous tile is consumed (and the queries are written before the first use)
-            for (int idx = threadIdx.x; idx < SA_KT * D; idx += blockDim.x) {
-                const int j = idx / D, d = idx - j * D;
+            // a warp fetches whole key rows: one block-table look-up per row, neighbouring lanes read neighbouring elements
+            for (int j = warp; j < SA_KT; j += SA_WARPS) {
                 const int key = k0 + j;
-                float kv = 0.0f;
+                const T* ksrc = nullptr;
+                const T* vsrc = nullptr;
                 if (key >= a && key < b) {
                     const int blk = bt[key / p.page];
                     if (blk >= 0 && blk < p.num_pages) {
-                        kv = to_float(kp[(((size_t)blk * p.G + kvh) * p.page + (key % p.page)) * D + d]);
-                    } else if (d == 0 && p.err) {
+                        const size_t row = ((size_t)blk * p.G + kvh) * p.page + (key % p.page);
+                        ksrc = kp + row * D;
+                        if (!alias) vsrc = vp + row * DV;
+                    } else if (lane == 0 && p.err) {
                         atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
                     }
                 }
-                Ks[j * DP + d] = kv;
-            }
-            if (!alias) {
-                for (int idx = threadIdx.x; idx < SA_KT * DV; idx += blockDim.x) {
-                    const int j = idx / DV, d = idx - j * DV;
-                    const int key = k0 + j;
-                    float vv = 0.0f;
-                    if (key >= a && key < b) {
-                        const int blk = bt[key / p.page];
-                        if (blk >= 0 && blk < p.num_pages)
-                            vv = to_float(vp[(((size_t)blk * p.G + kvh) * p.page + (key % p.page)) * DV + d]);
-                    }
-                    Vs[j * DV + d] = vv;
+                float* kd = Ks + j * DP;
+                for (int d = lane; d < D; d += 32) kd[d] = ksrc ? to_float(ksrc[d]) : 0.0f;
+                if (!alias) {
+                    float* vd = Vs + j * DV;
+                    for (int d = lane; d < DV; d += 32) vd[d] = vsrc ? to_float(vsrc[d]) : 0.0f;
                 }
             }
             __syncthreads();
 
+            // the warp's rows together: a key element read from shared memory serves all of them
+            float sc[SA_ROWS_PER_WARP];
+            const int key = k0 + lane;
+            const float* kr = Ks + lane * DP;
+#pragma unroll
+            for (int i = 0; i < SA_ROWS_PER_WARP; i++) sc[i] = 0.0f;
+            if (vec4) {
+                for (int d = 0; d < D; d += 4) {
+                    const float k0v = kr[d], k1v = kr[d + 1], k2v = kr[d + 2], k3v = kr[d + 3];
+#pragma unroll
+                    for (int i = 0; i < SA_ROWS_PER_WARP; i++) {
+                        const int r = warp + i * SA_WARPS;
+                        if (r < rows) {   // uniform per warp
+                            const float4 qv = *reinterpret_cast<const float4*>(Qs + r * D + d);
+                            sc[i] = fmaf(qv.x, k0v, sc[i]); sc[i] = fmaf(qv.y, k1v, sc[i]);
+                            sc[i] = fmaf(qv.z, k2v, sc[i]); sc[i] = fmaf(qv.w, k3v, sc[i]);
+                        }
+                    }
+                }
+            } else {
+                for (int d = 0; d < D; d++) {
+                    const float kv = kr[d];
+#pragma unroll
+                    for (int i = 0; i < SA_ROWS_PER_WARP; i++) {
+                        const int r = warp + i * SA_WARPS;
+                        if (r < rows) sc[i] = fmaf(Qs[r * D + d], kv, sc[i]);
+                    }
+                }
+            }
+            float pj[SA_ROWS_PER_WARP];
+            bool any = false;
 #pragma unroll
             for (int i = 0; i < SA_ROWS_PER_WARP; i++) {
                 const int r = warp + i * SA_WARPS;
+                pj[i] = 0.0f;
                 if (r >= rows) continue;  // uniform per warp
                 const int qpos = pos0 + r / nh;
-                const int key = k0 + lane;
                 const bool visible = key >= a && key < b && key <= qpos &&
                                      (p.window <= 0 || qpos - key < p.window || key < p.keep_first);
-                float s = 0.0f;
-                const float* qr = Qs + r * D;
-                const float* kr = Ks + lane * DP;
-                for (int d = 0; d < D; d++) s = fmaf(qr[d], kr[d], s);
-                s = visible ? s * p.scale : -INFINITY;
-                const float tmax = warp_max(s);
-                const float m_new = fmaxf(m[i], tmax);
+                const float sv = visible ? sc[i] * p.scale : -INFINITY;
+                const float m_new = fmaxf(m[i], warp_max(sv));
                 if (m_new == -INFINITY) continue;  // nothing visible so far (uniform per warp)
                 const float corr = expf(m[i] - m_new);
-                const float pj = visible ? expf(s - m_new) : 0.0f;
-                l[i] = l[i] * corr + warp_sum(pj);
+                pj[i] = visible ? expf(sv - m_new) : 0.0f;
+                l[i] = l[i] * corr + warp_sum(pj[i]);
                 m[i] = m_new;
+                any = true;
 #pragma unroll
                 for (int c = 0; c < NC; c++) acc[i][c] *= corr;
-                for (int j = 0; j < SA_KT; j++) {
-                    const float w = __shfl_sync(0xffffffffu, pj, j);
-                    const float* vr = Vs + j * vs_ld;
+            }
+            if (any) {
+                for (int jj = 0; jj < SA_KT; jj++) {
+                    float w[SA_ROWS_PER_WARP];
+#pragma unroll
+                    for (int i = 0; i < SA_ROWS_PER_WARP; i++) w[i] = __shfl_sync(0xffffffffu, pj[i], jj);
+                    const float* vr = Vs + jj * vs_ld;
 #pragma unroll
                     for (int c = 0; c < NC; c++) {
                         const int d = lane + 32 * c;
-                        if (d < DV) acc[i][c] = fmaf(w, vr[d], acc[i][c]);
+                        if (d < DV) {
+                            const float vv = vr[d];
+#pragma unroll
+                            for (int i = 0; i < SA_ROWS_PER_WARP; i++) acc[i][c] = fmaf(w[i], vv, acc[i][c]);
+                        }
                     }
                 }
             }

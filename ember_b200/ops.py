@@ -1054,3 +1054,27 @@ def moe_combine(y: torch.Tensor, wgt: torch.Tensor, slot_of_pair: torch.Tensor, 
     lib = _lib("moe")
     _call(lib, lib.ember_moe_combine, _p(y), _p(wgt), _p(slot_of_pair), c_int(T), c_int(top), _p(out), c_int(1 if accumulate else 0),
           c_int(hidden), _stream(stream))
+
+
+def moe_gather(x: torch.Tensor, pair_of_slot: torch.Tensor, n_pairs: int, top: int, xs: torch.Tensor, stream: Optional[int] = None) -> None:
+    """xs[slot] = x[token of the slot's pair]: every expert's rows side by side (rows of a multiple of 16 bytes)."""
+    _check(x, "x")
+    _check(xs, "xs", x.dtype)
+    _check(pair_of_slot, "pair_of_slot", torch.int32)
+    row = x.shape[-1] * x.element_size()
+    if xs.shape[-1] != x.shape[-1] or xs.numel() < n_pairs * x.shape[-1] or pair_of_slot.numel() < n_pairs:
+        raise KernelError("moe_gather: buffers do not fit the step")
+    lib = _lib("moe")
+    _call(lib, lib.ember_moe_gather, _p(x), _p(pair_of_slot), c_int(n_pairs), c_int(top), _p(xs), c_int(row), _stream(stream))
+
+
+def moe_activation(gu: torch.Tensor, act: torch.Tensor, rows: int, limit: float, alpha: float, stream: Optional[int] = None) -> None:
+    """act[r, j] = g sigmoid(alpha g) (u + 1) with g = min(gu[r, 2j], limit), u = clamp(gu[r, 2j + 1], -limit, limit); gu fp32."""
+    _check(gu, "gu", torch.float32)
+    _check(act, "act")
+    n = act.shape[-1]
+    if gu.shape[-1] != 2 * n or gu.numel() < rows * 2 * n or act.numel() < rows * n:
+        raise KernelError("moe_activation: buffers do not fit")
+    lib = _lib("moe")
+    _call(lib, lib.ember_moe_activation, _p(gu), _p(act), c_int(dtype_code(act.dtype)), c_longlong(rows * n), c_float(limit),
+          c_float(alpha), _stream(stream))

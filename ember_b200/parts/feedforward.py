@@ -64,10 +64,17 @@ class RoutedMLP(FeedForward):
     is the first product's epilogue) and the down matrices as [experts, hidden, ff].  The step's (token, choice) pairs
     are ordered by expert on the device; both products walk row tiles of one expert each, so every expert's weights
     are read once per step however the tokens fall, and nothing comes back to the host (decode steps are captured
-    into CUDA graphs like any other).  Tensors under the prefix: router, e<i>.gate, e<i>.up, e<i>.down."""
+    into CUDA graphs like any other).
+
+    A bfloat16 step of more tokens than any captured step has (a prompt portion) takes the tensor cores instead: the
+    tokens' rows are gathered expert by expert, the host reads the experts' row counts (the step's one look at the
+    device) and every expert with rows runs the tcgen05 product on its slice, first gate/up into fp32, an element-wise
+    kernel for the clamped activation, then down; the weighted sum over a token's choices is the same kernel either way.
+    Tensors under the prefix: router, e<i>.gate, e<i>.up, e<i>.down."""
 
     graph_safe = True
     can_store = True
+    TC_MIN_TOKENS = 257          # more runs than a captured decode step can have: such a step is never inside a graph
 
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
@@ -106,6 +113,13 @@ class RoutedMLP(FeedForward):
             down[e] = rt.to_device(got[f"{p}e{e}.down"], wd)
         self.gate_up = gu.view(s.experts, 2 * s.intermediate_size, s.hidden_size)
         self.down = down
+        if wd == torch.bfloat16:
+            ops.reserve_scratch(rt.device, 128 * max(2 * s.intermediate_size, s.hidden_size))    # (the small-M product's)
+
+    def _on_tensor_cores(self, ctx, x) -> bool:
+        s = self.spec
+        return (ops.TC_ENABLED and x.dtype == torch.bfloat16 and ctx.T >= self.TC_MIN_TOKENS and s.hidden_size % 8 == 0
+                and s.intermediate_size % 8 == 0)
 
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
         s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
@@ -124,8 +138,23 @@ class RoutedMLP(FeedForward):
         self.router(ctx, x, logits, T, ops.EPI_STORE_F32)
         ops.moe_route(logits, T, top, sel, wgt, stream=ctx.stream)
         max_tiles = ops.moe_group(sel, pairs, E, offsets, pair_of_slot, slot_of_pair, tiles, stream=ctx.stream)
-        ops.moe_gemm(x, self.gate_up, act, offsets, pair_of_slot, tiles, max_tiles, top, True, s.limit, s.alpha, stream=ctx.stream)
-        ops.moe_gemm(act, self.down, y, offsets, pair_of_slot, tiles, max_tiles, 0, False, stream=ctx.stream)
+        if self._on_tensor_cores(ctx, x):
+            xs = ctx.buf("routed_mlp.gathered", (mt * top, s.hidden_size), rt.dtype)
+            gu = ctx.buf("routed_mlp.gate_up", (mt * top, 2 * s.intermediate_size), torch.float32)
+            ops.moe_gather(x, pair_of_slot, pairs, top, xs, stream=ctx.stream)
+            bounds = offsets.tolist()                      # the experts' row ranges: the host waits for the grouping here
+            for e in range(E):
+                lo, n = bounds[e], bounds[e + 1] - bounds[e]
+                if n > 0:
+                    ops.gemm_tc(xs[lo:lo + n], self.gate_up[e], gu[lo:lo + n], n, ops.EPI_STORE_F32, err=ctx.err, stream=ctx.stream)
+            ops.moe_activation(gu, act, pairs, s.limit, s.alpha, stream=ctx.stream)
+            for e in range(E):
+                lo, n = bounds[e], bounds[e + 1] - bounds[e]
+                if n > 0:
+                    ops.gemm_tc(act[lo:lo + n], self.down[e], y[lo:lo + n], n, ops.EPI_STORE_F32, err=ctx.err, stream=ctx.stream)
+        else:
+            ops.moe_gemm(x, self.gate_up, act, offsets, pair_of_slot, tiles, max_tiles, top, True, s.limit, s.alpha, stream=ctx.stream)
+            ops.moe_gemm(act, self.down, y, offsets, pair_of_slot, tiles, max_tiles, 0, False, stream=ctx.stream)
         ops.moe_combine(y, wgt, slot_of_pair, T, top, residual, accumulate=accumulate, stream=ctx.stream)
 
 
