@@ -1,6 +1,7 @@
 // Routed feed-forward (mixture of experts) over a step's tokens.
 //
 //   route:    per token the `top` largest router logits (ties: the lower index), weights = softmax over those alone;
+//             `router` also makes the logits itself (fp32 weights, fp32 sums), a warp a token;
 //   group:    the (token, choice) pairs ordered by expert: per-expert counts and offsets, the pair behind every
 //             slot, the slot of every pair, and the list of (expert, first slot) row tiles the products walk;
 //   gate_up:  act[slot] = f(W_gu[e] x[token]) for the slots of expert e, the rows of gate and up interleaved so that a
@@ -8,6 +9,10 @@
 //             f = g sigmoid(alpha g) (u + 1);
 //   down:     y[slot] = W_down[e] act[slot]  (fp32);
 //   combine:  out[token] = sum over its choices, in order, of weight * y[slot]  (stored, or added to what is there).
+// Both products come in two forms: tiles of 32 slots x 64 outputs through shared memory (any sizes, any step), and,
+// for steps of few tokens, a streaming form in which a block keeps its (at most 16) rows in shared memory and every
+// warp streams whole weight rows past them in 16-byte pieces, so an expert's weights are read once at the rate of
+// the memory and only the rows that exist are multiplied.
 //
 // Nothing is read back by the host: the products' grids are sized for the most row tiles the step can have and blocks
 // beyond the tile list leave at once, so a decode step can be captured into a CUDA graph.  Every output row is a sum
@@ -22,7 +27,10 @@ namespace ember {
 constexpr int MOE_MAX_EXPERTS = 256;
 constexpr int MOE_BM = 32, MOE_BN = 64, MOE_BK = 16;
 
-// One warp a token.  A lane holds experts lane, lane + 32, ...
+// One warp a token.  A lane holds experts lane, lane + 32, ... in z.
+__device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32], int E, int top, int* __restrict__ sel,
+                                               float* __restrict__ wgt, int t, int lane);
+
 __global__ void moe_route_kernel(const float* __restrict__ logits, int E, int top, int* __restrict__ sel,
                                  float* __restrict__ wgt, int T) {
     pdl_launch_dependents();
@@ -35,6 +43,51 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int E, int to
         const int e = lane + 32 * i;
         z[i] = e < E ? logits[(size_t)t * E + e] : -INFINITY;
     }
+    choose_experts(z, E, top, sel, wgt, t, lane);
+}
+
+// The router's product and the choice in one: logits[e] = sum_k x[t, k] w[e, k] with fp32 weights and sums.  A block
+// a token: its warps share the experts (four elements a lane and load), the first warp then chooses.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ x, const float* __restrict__ w, int K, int E, int top,
+                                                         int* __restrict__ sel, float* __restrict__ wgt, float* __restrict__ logits) {
+    __shared__ float zs[MOE_MAX_EXPERTS];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const T* row = x + (size_t)t * K;
+    const bool vec = (K & 3) == 0;
+    for (int e = warp; e < E; e += nw) {
+        const float* we = w + (size_t)e * K;
+        float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        if (vec) {
+            for (int k = 4 * lane; k < K; k += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(we + k);
+                s0 = fmaf(to_float(row[k]), wv.x, s0); s1 = fmaf(to_float(row[k + 1]), wv.y, s1);
+                s2 = fmaf(to_float(row[k + 2]), wv.z, s2); s3 = fmaf(to_float(row[k + 3]), wv.w, s3);
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) s0 = fmaf(to_float(row[k]), we[k], s0);
+        }
+        const float s = warp_sum((s0 + s1) + (s2 + s3));
+        if (lane == 0) {
+            zs[e] = s;
+            if (logits) logits[(size_t)t * E + e] = s;
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float z[MOE_MAX_EXPERTS / 32];
+#pragma unroll
+    for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+        const int e = lane + 32 * i;
+        z[i] = e < E ? zs[e] : -INFINITY;
+    }
+    choose_experts(z, E, top, sel, wgt, t, lane);
+}
+
+__device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32], int E, int top, int* __restrict__ sel,
+                                               float* __restrict__ wgt, int t, int lane) {
     float first = 0.0f, sum = 0.0f, mine = 0.0f;            // lane k keeps the k-th choice's weight (top <= 32)
     for (int k = 0; k < top; k++) {
         float best = -INFINITY;
@@ -70,7 +123,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int E, int to
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ sel, int n_pairs, int E, int* __restrict__ offsets,
                                                          int* __restrict__ pair_of_slot, int* __restrict__ slot_of_pair,
                                                          int* __restrict__ n_tiles, int* __restrict__ tile_expert,
-                                                         int* __restrict__ tile_row0, int max_tiles) {
+                                                         int* __restrict__ tile_row0, int max_tiles, int tile_rows) {
     __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS + 1], cursor[MOE_MAX_EXPERTS], tstart[MOE_MAX_EXPERTS + 1];
     pdl_launch_dependents();
     pdl_wait();
@@ -83,7 +136,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
         for (int e = 0; e < E; e++) {
             start[e] = at; tstart[e] = tt;
             at += count[e];
-            tt += (count[e] + MOE_BM - 1) / MOE_BM;
+            tt += (count[e] + tile_rows - 1) / tile_rows;
         }
         start[E] = at; tstart[E] = tt;
         *n_tiles = tt < max_tiles ? tt : max_tiles;
@@ -104,7 +157,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
         for (int j = 0; j < n; j++)
             if (tstart[e] + j < max_tiles) {
                 tile_expert[tstart[e] + j] = e;
-                tile_row0[tstart[e] + j] = start[e] + j * MOE_BM;
+                tile_row0[tstart[e] + j] = start[e] + j * tile_rows;
             }
     }
 }
@@ -189,6 +242,99 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(MoeGemmArgs p) {
     }
 }
 
+// ------------------------------------------------------------------------- the streaming form (few rows a tile)
+constexpr int MS_ROWS = 16, MS_WARPS = 8, MS_PAIRS = 32;      // rows a tile, warps a block, column pairs a block
+
+template <typename T>
+struct Piece;                                                 // 16 bytes of a row as floats
+template <>
+struct Piece<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void unpack(const uint4& v, float* f) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    }
+};
+template <>
+struct Piece<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void unpack(const uint4& v, float* f) {
+        f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+        f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+        f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+        f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+    }
+};
+
+template <typename T, typename TO, bool GATED, int R>
+__device__ __forceinline__ void moe_stream_rows(const MoeGemmArgs& p, const uint4* xs, const T* w, int row0, int rows, int pair0) {
+    constexpr int PN = Piece<T>::N;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int k16 = p.K / PN;                                  // 16-byte pieces a row
+    const int n_pairs = (p.N + 1) / 2;
+    for (int pr = pair0 + warp; pr < min(pair0 + MS_PAIRS, n_pairs); pr += MS_WARPS) {
+        const int n0 = 2 * pr;
+        const bool two = n0 + 1 < p.N;
+        const uint4* w0 = reinterpret_cast<const uint4*>(w + (size_t)n0 * p.K);
+        const uint4* w1 = reinterpret_cast<const uint4*>(w + (size_t)(two ? n0 + 1 : n0) * p.K);
+        float a0[R], a1[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) { a0[r] = 0.0f; a1[r] = 0.0f; }
+#pragma unroll 2
+        for (int k = lane; k < k16; k += 32) {
+            float f0[PN], f1[PN];
+            Piece<T>::unpack(__ldg(w0 + k), f0);
+            Piece<T>::unpack(__ldg(w1 + k), f1);
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                float xf[PN];
+                Piece<T>::unpack(xs[(size_t)r * k16 + k], xf);
+#pragma unroll
+                for (int i = 0; i < PN; i++) { a0[r] = fmaf(f0[i], xf[i], a0[r]); a1[r] = fmaf(f1[i], xf[i], a1[r]); }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) { a0[r] = warp_sum(a0[r]); a1[r] = warp_sum(a1[r]); }
+        // lane r writes row r
+        float v0 = 0.0f, v1 = 0.0f;
+#pragma unroll
+        for (int r = 0; r < R; r++)
+            if (lane == r) { v0 = a0[r]; v1 = a1[r]; }
+        if (lane < rows) {
+            TO* o = (TO*)p.out + (size_t)(row0 + lane) * p.ld_o;
+            if (GATED) {
+                const float g = fminf(v0, p.limit), u = fminf(fmaxf(v1, -p.limit), p.limit);
+                o[pr] = from_float<TO>(g / (1.0f + expf(-p.alpha * g)) * (u + 1.0f));
+            } else {
+                o[n0] = from_float<TO>(v0);
+                if (two) o[n0 + 1] = from_float<TO>(v1);
+            }
+        }
+    }
+}
+
+template <typename T, typename TO, bool GATED>
+__global__ void __launch_bounds__(MS_WARPS * 32) moe_stream_kernel(MoeGemmArgs p) {
+    extern __shared__ uint4 xs[];                              // [MS_ROWS][K] of T
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)blockIdx.x >= *p.n_tiles) return;
+    const int e = p.tile_expert[blockIdx.x], row0 = p.tile_row0[blockIdx.x];
+    const int rows = min(MS_ROWS, p.offsets[e + 1] - row0);
+    const int k16 = p.K / Piece<T>::N;
+    for (int idx = threadIdx.x; idx < rows * k16; idx += blockDim.x) {
+        const int r = idx / k16, k = idx - r * k16;
+        const int src = p.top > 0 ? p.pair_of_slot[row0 + r] / p.top : row0 + r;
+        xs[idx] = reinterpret_cast<const uint4*>((const T*)p.x + (size_t)src * p.ld_x)[k];
+    }
+    __syncthreads();
+    const T* w = (const T*)p.w + (size_t)e * p.w_expert;
+    const int pair0 = blockIdx.y * MS_PAIRS;
+    if (rows <= 2) moe_stream_rows<T, TO, GATED, 2>(p, xs, w, row0, rows, pair0);
+    else if (rows <= 4) moe_stream_rows<T, TO, GATED, 4>(p, xs, w, row0, rows, pair0);
+    else if (rows <= 8) moe_stream_rows<T, TO, GATED, 8>(p, xs, w, row0, rows, pair0);
+    else moe_stream_rows<T, TO, GATED, 16>(p, xs, w, row0, rows, pair0);
+}
+
 // xs[slot] = x[token of the slot's pair]: the rows of each expert side by side, for products that want plain matrices.
 __global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ pair_of_slot, int top, uint4* __restrict__ xs,
                                   int row16) {
@@ -239,12 +385,27 @@ EMBER_API int ember_moe_route(const float* logits, int T, int E, int top, int* s
     return check_launch("moe_route");
 }
 
+EMBER_API int ember_moe_router(const void* x, int x_dtype, const float* w, int T, int K, int E, int top, int* sel, float* wgt,
+                               float* logits, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || top > 32 || K <= 0)
+        return fail("moe_router: top %d of %d experts (at most 32 of %d), rows of %d", top, E, MOE_MAX_EXPERTS, K);
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned threads = E >= 8 ? 256 : 32 * E;           // a warp an expert, up to eight
+    if (x_dtype == EMBER_F32) launch_kernel(moe_router_kernel<float>, T, threads, 0, st, (const float*)x, w, K, E, top, sel, wgt, logits);
+    else if (x_dtype == EMBER_BF16)
+        launch_kernel(moe_router_kernel<__nv_bfloat16>, T, threads, 0, st, (const __nv_bfloat16*)x, w, K, E, top, sel, wgt, logits);
+    else return fail("moe_router: unsupported dtype %d", x_dtype);
+    return check_launch("moe_router");
+}
+
 EMBER_API int ember_moe_group(const int* sel, int n_pairs, int E, int* offsets, int* pair_of_slot, int* slot_of_pair, int* n_tiles,
-                              int* tile_expert, int* tile_row0, int max_tiles, void* stream) {
+                              int* tile_expert, int* tile_row0, int max_tiles, int tile_rows, void* stream) {
     if (n_pairs <= 0) return 0;
-    if (E <= 0 || E > MOE_MAX_EXPERTS || max_tiles < n_pairs / MOE_BM + E) return fail("moe_group: %d experts, room for %d tiles", E, max_tiles);
+    if (tile_rows != MOE_BM && tile_rows != MS_ROWS) return fail("moe_group: tiles of %d rows (%d or %d)", tile_rows, MOE_BM, MS_ROWS);
+    if (E <= 0 || E > MOE_MAX_EXPERTS || max_tiles < n_pairs / tile_rows + E) return fail("moe_group: %d experts, room for %d tiles", E, max_tiles);
     launch_kernel(moe_group_kernel, 1, 1024, 0, (cudaStream_t)stream, sel, n_pairs, E, offsets, pair_of_slot, slot_of_pair, n_tiles,
-                  tile_expert, tile_row0, max_tiles);
+                  tile_expert, tile_row0, max_tiles, tile_rows);
     return check_launch("moe_group");
 }
 
@@ -268,6 +429,42 @@ EMBER_API int ember_moe_gemm(const void* x, int x_dtype, int ld_x, const void* w
         else return fail("moe_gemm: unsupported dtypes %d", key);
     }
     return check_launch("moe_gemm");
+}
+
+// The streaming form of ember_moe_gemm, for tile lists made with tiles of 16 rows.  Rows of x and of the weights must
+// be multiples of 16 bytes, and 16 rows of x must fit in shared memory.
+EMBER_API int ember_moe_stream_rows() { return MS_ROWS; }
+
+EMBER_API int ember_moe_stream(const void* x, int x_dtype, int ld_x, const void* w, int w_dtype, long long w_expert, void* out,
+                               int out_dtype, int ld_o, const int* offsets, const int* pair_of_slot, const int* n_tiles,
+                               const int* tile_expert, const int* tile_row0, int max_tiles, int top, int N, int K, int gated,
+                               float limit, float alpha, void* stream) {
+    if (max_tiles <= 0) return 0;
+    if (N <= 0 || K <= 0 || (gated && (N & 1))) return fail("moe_stream: N=%d K=%d", N, K);
+    const int elem = x_dtype == EMBER_F32 ? 4 : 2;
+    if (((size_t)K * elem) % 16 || ((size_t)ld_x * elem) % 16) return fail("moe_stream: rows of %d elements are no multiple of 16 bytes", K);
+    const size_t smem = (size_t)MS_ROWS * K * elem;
+    if (smem > 200 * 1024) return fail("moe_stream: %d rows of %d do not fit in shared memory", MS_ROWS, K);
+    MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha};
+    dim3 grid(max_tiles, ((N + 1) / 2 + MS_PAIRS - 1) / MS_PAIRS);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int key = x_dtype * 100 + w_dtype * 10 + out_dtype;       // F32 = 0, BF16 = 1
+    auto run = [&](auto kernel) -> int {
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return fail("moe_stream: shared memory %zu: %s", smem, cudaGetErrorString(e));
+        }
+        launch_kernel(kernel, grid, MS_WARPS * 32, smem, st, p);
+        return check_launch("moe_stream");
+    };
+    if (gated) {
+        if (key == 0) return run(moe_stream_kernel<float, float, true>);
+        if (key == 111) return run(moe_stream_kernel<__nv_bfloat16, __nv_bfloat16, true>);
+    } else {
+        if (key == 0) return run(moe_stream_kernel<float, float, false>);
+        if (key == 110) return run(moe_stream_kernel<__nv_bfloat16, float, false>);
+    }
+    return fail("moe_stream: unsupported dtypes %d", key);
 }
 
 EMBER_API int ember_moe_gather(const void* x, const int* pair_of_slot, int n_pairs, int top, void* xs, int row_bytes, void* stream) {

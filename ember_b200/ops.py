@@ -982,13 +982,20 @@ def sink_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch
 
 
 # --------------------------------------------------------------------- routed feed-forward (csrc/moe.cu)
-MOE_TILE_ROWS = 32               # slots of one expert a block of the grouped products takes (its MOE_BM)
+MOE_TILE_ROWS = 32               # slots of one expert a block of the tiled products takes (its MOE_BM)
+MOE_STREAM_ROWS = 16             # ... and a block of the streaming products (its MS_ROWS)
 MOE_MAX_EXPERTS, MOE_MAX_TOP = 256, 32
 
 
-def moe_max_tiles(n_pairs: int, experts: int) -> int:
+def moe_max_tiles(n_pairs: int, experts: int, tile_rows: int = MOE_TILE_ROWS) -> int:
     """The most row tiles a step of ``n_pairs`` (token, choice) pairs can have: every expert may end in a ragged tile."""
-    return n_pairs // MOE_TILE_ROWS + experts
+    return n_pairs // tile_rows + experts
+
+
+def moe_stream_usable(x: torch.Tensor, K: int) -> bool:
+    """Whether the streaming products take rows of ``K`` elements of x's type: multiples of 16 bytes, 16 of them in
+    shared memory."""
+    return (K * x.element_size()) % 16 == 0 and MOE_STREAM_ROWS * K * x.element_size() <= 200 * 1024
 
 
 def moe_route(logits: torch.Tensor, T: int, top: int, sel: torch.Tensor, wgt: torch.Tensor, stream: Optional[int] = None) -> None:
@@ -1004,29 +1011,30 @@ def moe_route(logits: torch.Tensor, T: int, top: int, sel: torch.Tensor, wgt: to
 
 
 def moe_group(sel: torch.Tensor, n_pairs: int, experts: int, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
-              slot_of_pair: torch.Tensor, tiles: torch.Tensor, stream: Optional[int] = None) -> int:
+              slot_of_pair: torch.Tensor, tiles: torch.Tensor, tile_rows: int = MOE_TILE_ROWS, stream: Optional[int] = None) -> int:
     """Orders the (token, choice) pairs by expert.  offsets int32 [experts + 1]; pair_of_slot, slot_of_pair int32
-    [n_pairs]; tiles int32 [1 + 2 max_tiles]: the number of row tiles, then every tile's expert, then every tile's
-    first slot.  Returns max_tiles (what the products' grids are sized for)."""
+    [n_pairs]; tiles int32 [1 + 2 max_tiles]: the number of row tiles (of up to ``tile_rows`` slots of one expert),
+    then every tile's expert, then every tile's first slot.  Returns max_tiles (what the products' grids are sized for)."""
     for t, n in ((sel, "sel"), (offsets, "offsets"), (pair_of_slot, "pair_of_slot"), (slot_of_pair, "slot_of_pair"), (tiles, "tiles")):
         _check(t, n, torch.int32)
-    mt = moe_max_tiles(n_pairs, experts)
+    mt = moe_max_tiles(n_pairs, experts, tile_rows)
     if sel.numel() < n_pairs or offsets.numel() < experts + 1 or pair_of_slot.numel() < n_pairs or slot_of_pair.numel() < n_pairs or \
             tiles.numel() < 1 + 2 * mt:
         raise KernelError("moe_group: buffers do not fit the step")
     lib = _lib("moe")
     _call(lib, lib.ember_moe_group, _p(sel), c_int(n_pairs), c_int(experts), _p(offsets), _p(pair_of_slot), _p(slot_of_pair),
-          _off(tiles, 0), _off(tiles, 1), _off(tiles, 1 + mt), c_int(mt), _stream(stream))
+          _off(tiles, 0), _off(tiles, 1), _off(tiles, 1 + mt), c_int(mt), c_int(tile_rows), _stream(stream))
     return mt
 
 
 def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
              tiles: torch.Tensor, max_tiles: int, top: int, gated: bool, limit: float = 0.0, alpha: float = 1.0,
-             stream: Optional[int] = None) -> None:
+             stream: Optional[int] = None, streaming: bool = False) -> None:
     """The product of every slot's row with its expert's matrix (``w`` [experts, N, K]).  ``top`` > 0: a slot's row of
     ``x`` is its token's (x [tokens, K], gathered through the pairs); 0: x has a row per slot.  ``gated``: w's rows are
     interleaved (gate, up) and out[slot, j] = g sigmoid(alpha g) (u + 1) with g = min(gate, limit),
-    u = clamp(up, -limit, limit), in x's dtype; else out[slot] is the fp32 product."""
+    u = clamp(up, -limit, limit), in x's dtype; else out[slot] is the fp32 product.  ``streaming``: the form for tile
+    lists of 16-row tiles (``moe_group`` with ``MOE_STREAM_ROWS``), else the form for 32-row tiles."""
     _check(x, "x")
     _check(w, "w", x.dtype)
     _check(out, "out", x.dtype if gated else torch.float32)
@@ -1035,7 +1043,7 @@ def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch
     if x.shape[-1] != K or out.shape[-1] != n_out:
         raise KernelError(f"moe_gemm: rows of {x.shape[-1]} -> {out.shape[-1]} against experts {tuple(w.shape)}")
     lib = _lib("moe")
-    _call(lib, lib.ember_moe_gemm, _p(x), c_int(dtype_code(x.dtype)), c_int(K), _p(w), c_int(dtype_code(w.dtype)), c_longlong(N * K),
+    _call(lib, lib.ember_moe_stream if streaming else lib.ember_moe_gemm, _p(x), c_int(dtype_code(x.dtype)), c_int(K), _p(w), c_int(dtype_code(w.dtype)), c_longlong(N * K),
           _p(out), c_int(dtype_code(out.dtype)), c_int(n_out), _p(offsets), _p(pair_of_slot), _off(tiles, 0), _off(tiles, 1),
           _off(tiles, 1 + max_tiles), c_int(max_tiles), c_int(top), c_int(N), c_int(K), c_int(1 if gated else 0), c_float(limit),
           c_float(alpha), _stream(stream))
@@ -1078,3 +1086,23 @@ def moe_activation(gu: torch.Tensor, act: torch.Tensor, rows: int, limit: float,
     lib = _lib("moe")
     _call(lib, lib.ember_moe_activation, _p(gu), _p(act), c_int(dtype_code(act.dtype)), c_longlong(rows * n), c_float(limit),
           c_float(alpha), _stream(stream))
+
+
+def moe_router(x: torch.Tensor, w: torch.Tensor, T: int, top: int, sel: torch.Tensor, wgt: torch.Tensor,
+               logits: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """The router's logits x[t] . w[e] (``w`` fp32 [experts, K], fp32 sums) and ``moe_route`` on them in one kernel;
+    ``logits`` (fp32 [T, experts]) receives them if given."""
+    _check(x, "x")
+    _check(w, "w", torch.float32)
+    _check(sel, "sel", torch.int32)
+    _check(wgt, "wgt", torch.float32)
+    E, K = w.shape
+    if x.shape[-1] != K or x.numel() < T * K or sel.numel() < T * top or wgt.numel() < T * top:
+        raise KernelError("moe_router: buffers do not fit the step")
+    if logits is not None:
+        _check(logits, "logits", torch.float32)
+        if logits.numel() < T * E:
+            raise KernelError("moe_router: the logits do not fit")
+    lib = _lib("moe")
+    _call(lib, lib.ember_moe_router, _p(x), c_int(dtype_code(x.dtype)), _p(w), c_int(T), c_int(K), c_int(E), c_int(top), _p(sel),
+          _p(wgt), _p(logits), _stream(stream))

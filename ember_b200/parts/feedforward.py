@@ -75,6 +75,7 @@ class RoutedMLP(FeedForward):
     graph_safe = True
     can_store = True
     TC_MIN_TOKENS = 257          # more runs than a captured decode step can have: such a step is never inside a graph
+    STREAM_MAX_TOKENS = 256      # up to here the products stream the weights past the few rows of a tile
 
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
@@ -104,7 +105,7 @@ class RoutedMLP(FeedForward):
         wd = rt.weight_dtype(got[f"{p}e0.gate"].dtype)
         if wd != rt.dtype:
             wd = torch.float32 if rt.dtype == torch.float32 else torch.bfloat16
-        self.router = Linear(rt.to_device(got[p + "router"], torch.float32))
+        self.router = rt.to_device(got[p + "router"], torch.float32)
         gu = torch.empty((s.experts, s.intermediate_size, 2, s.hidden_size), dtype=wd, device=rt.device)
         down = torch.empty((s.experts, s.hidden_size, s.intermediate_size), dtype=wd, device=rt.device)
         for e in range(s.experts):
@@ -126,18 +127,19 @@ class RoutedMLP(FeedForward):
         E, top, pairs = s.experts, s.top, ctx.T * s.top
         if x.dtype != self.gate_up.dtype:
             raise ops.KernelError(f"routed feed-forward: input {x.dtype} against experts {self.gate_up.dtype}")
-        logits = ctx.buf("routed_mlp.logits", (mt, E), torch.float32)
         sel = ctx.buf("routed_mlp.sel", (mt * top,), torch.int32)
         wgt = ctx.buf("routed_mlp.weights", (mt * top,), torch.float32)
         offsets = ctx.buf("routed_mlp.offsets", (E + 1,), torch.int32)
         pair_of_slot = ctx.buf("routed_mlp.pair_of_slot", (mt * top,), torch.int32)
         slot_of_pair = ctx.buf("routed_mlp.slot_of_pair", (mt * top,), torch.int32)
-        tiles = ctx.buf("routed_mlp.tiles", (1 + 2 * ops.moe_max_tiles(mt * top, E),), torch.int32)
+        tiles = ctx.buf("routed_mlp.tiles", (1 + 2 * ops.moe_max_tiles(mt * top, E, ops.MOE_STREAM_ROWS),), torch.int32)
         act = ctx.buf("routed_mlp.act", (mt * top, s.intermediate_size), rt.dtype)
         y = ctx.buf("routed_mlp.down", (mt * top, s.hidden_size), torch.float32)
-        self.router(ctx, x, logits, T, ops.EPI_STORE_F32)
-        ops.moe_route(logits, T, top, sel, wgt, stream=ctx.stream)
-        max_tiles = ops.moe_group(sel, pairs, E, offsets, pair_of_slot, slot_of_pair, tiles, stream=ctx.stream)
+        ops.moe_router(x, self.router, T, top, sel, wgt, stream=ctx.stream)
+        streaming = (T <= self.STREAM_MAX_TOKENS and ops.moe_stream_usable(x, s.hidden_size)
+                     and ops.moe_stream_usable(x, s.intermediate_size))
+        max_tiles = ops.moe_group(sel, pairs, E, offsets, pair_of_slot, slot_of_pair, tiles,
+                                  ops.MOE_STREAM_ROWS if streaming else ops.MOE_TILE_ROWS, stream=ctx.stream)
         if self._on_tensor_cores(ctx, x):
             xs = ctx.buf("routed_mlp.gathered", (mt * top, s.hidden_size), rt.dtype)
             gu = ctx.buf("routed_mlp.gate_up", (mt * top, 2 * s.intermediate_size), torch.float32)
@@ -153,8 +155,9 @@ class RoutedMLP(FeedForward):
                 if n > 0:
                     ops.gemm_tc(act[lo:lo + n], self.down[e], y[lo:lo + n], n, ops.EPI_STORE_F32, err=ctx.err, stream=ctx.stream)
         else:
-            ops.moe_gemm(x, self.gate_up, act, offsets, pair_of_slot, tiles, max_tiles, top, True, s.limit, s.alpha, stream=ctx.stream)
-            ops.moe_gemm(act, self.down, y, offsets, pair_of_slot, tiles, max_tiles, 0, False, stream=ctx.stream)
+            ops.moe_gemm(x, self.gate_up, act, offsets, pair_of_slot, tiles, max_tiles, top, True, s.limit, s.alpha, stream=ctx.stream,
+                         streaming=streaming)
+            ops.moe_gemm(act, self.down, y, offsets, pair_of_slot, tiles, max_tiles, 0, False, stream=ctx.stream, streaming=streaming)
         ops.moe_combine(y, wgt, slot_of_pair, T, top, residual, accumulate=accumulate, stream=ctx.stream)
 
 

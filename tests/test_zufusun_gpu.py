@@ -398,6 +398,17 @@ def test_the_router_chooses_and_weighs_like_the_plain_implementation():
     assert sel.view(T, top).cpu().tolist() == idx[:, :top].tolist()
     assert torch.allclose(wgt.view(T, top).cpu().double(), torch.softmax(val[:, :top], -1), atol=1e-6)
     assert sel.view(T, top)[7, :2].tolist() == [3, 20] and sel.view(T, top)[8].tolist() == list(range(top))
+    # the kernel that makes the logits itself (fp32 weights and sums) chooses the same way
+    for xdt in (torch.float32, torch.bfloat16):
+        x = torch.randn(T, 72, generator=torch.Generator().manual_seed(2)).to(xdt)
+        w = torch.randn(E, 72, generator=torch.Generator().manual_seed(3))
+        sel2, wgt2 = torch.zeros_like(sel), torch.zeros_like(wgt)
+        lg = torch.zeros(T, E, device=dev)
+        ops.moe_router(x.to(dev), w.to(dev), T, top, sel2, wgt2, logits=lg)
+        assert torch.allclose(lg.cpu().double(), x.double() @ w.double().T, atol=1e-4)
+        v2, i2 = torch.sort(lg.cpu().double(), dim=-1, descending=True, stable=True)
+        assert sel2.view(T, top).cpu().tolist() == i2[:, :top].tolist()
+        assert torch.allclose(wgt2.view(T, top).cpu().double(), torch.softmax(v2[:, :top], -1), atol=1e-6)
     offsets = torch.zeros(E + 1, dtype=torch.int32, device=dev)
     pair_of_slot = torch.zeros(T * top, dtype=torch.int32, device=dev)
     slot_of_pair = torch.zeros(T * top, dtype=torch.int32, device=dev)
