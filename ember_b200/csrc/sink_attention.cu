@@ -511,6 +511,216 @@ int launch_sink_attention(const SinkAttnParams& p, int n_tiles, int T_tokens, cu
     return 0;
 }
 
+
+// ------------------------------------------------- attention over shared key rows on the tensor cores (bfloat16)
+// For the layout in which one cached row serves every query head as key and, with its first DV elements, as value
+// (no value pool).  A block takes 64 (query, head) rows and walks the visible keys 32 at a time: scores
+// S = Q K^T and O += P V on mma.sync m16n8k16 (bf16 operands, fp32 accumulators), the softmax with its running maximum,
+// denominators and the sink in fp32 registers.  Eight warps: warp (wr, wc) owns rows 16 wr .. 16 wr + 15 and the
+// half wc of the value columns; both warps of a row slab compute the slab's scores (the same numbers), so no
+// exchange is needed.  P enters the second product rounded to bfloat16, as V is.
+constexpr int LT_ROWS = 64, LT_KT = 32, LT_PAD = 8;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// NTO: value-column tiles of 8 a warp owns (DV / 2 <= 8 NTO).
+template <typename TO, int NTO>
+__global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAttnParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int D = p.D, DV = p.DV, DP = D + LT_PAD;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][DP]
+    __nv_bfloat16* Ks = Qs + LT_ROWS * DP;                                      // [32][DP]
+    const int group = p.H / p.G;
+    const int chunks = (group + p.head_chunk - 1) / p.head_chunk;
+    const int tile = blockIdx.x, kvh = blockIdx.y / chunks, hc = blockIdx.y - kvh * chunks;
+    const int head0 = kvh * group + hc * p.head_chunk;
+    const int nh = min(p.head_chunk, group - hc * p.head_chunk);
+    const int seq = p.tiles[tile * 4 + 0], row0 = p.tiles[tile * 4 + 1], nq = p.tiles[tile * 4 + 2], pos0 = p.tiles[tile * 4 + 3];
+    const int rows = nq * nh;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wr = warp & 3, wc = warp >> 2;
+    const int g = lane >> 2, t = lane & 3;
+    const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
+    const __nv_bfloat16* kp = (const __nv_bfloat16*)p.k_pool;
+    const int d8 = D / 8;
+
+    for (int idx = threadIdx.x; idx < LT_ROWS * d8; idx += blockDim.x) {
+        const int r = idx / d8, c = idx - r * d8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < rows) {
+            const int qi = r / nh, gq = r - qi * nh;
+            v = reinterpret_cast<const uint4*>(q + ((size_t)(row0 + qi) * p.H + head0 + gq) * D)[c];
+        }
+        *reinterpret_cast<uint4*>(Qs + r * DP + c * 8) = v;
+    }
+
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int hi = pos0 + nq;
+    const int kept = p.window > 0 ? min(p.keep_first, lo) : 0;
+    const int rA = wr * 16 + g, rB = rA + 8;                   // the thread's two rows
+    const int qposA = pos0 + rA / nh, qposB = pos0 + rB / nh;
+    const bool liveA = rA < rows, liveB = rB < rows;
+    const int half = DV / 2, col0 = wc * half;                 // the warp's value columns
+
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.0f, lB = 0.0f;
+    float o[NTO][4];
+#pragma unroll
+    for (int i = 0; i < NTO; i++) { o[i][0] = 0.0f; o[i][1] = 0.0f; o[i][2] = 0.0f; o[i][3] = 0.0f; }
+
+    const int* bt = p.block_table + (size_t)seq * p.max_blocks;
+    for (int part = 0; part < 2; part++) {
+        const int a = part == 0 ? 0 : lo, b = part == 0 ? kept : hi;
+        if (a >= b) continue;
+        for (int k0 = a - (a % LT_KT); k0 < b; k0 += LT_KT) {
+            __syncthreads();
+            for (int j = warp; j < LT_KT; j += 8) {
+                const int key = k0 + j;
+                const uint4* src = nullptr;
+                if (key >= a && key < b) {
+                    const int blk = bt[key / p.page];
+                    if (blk >= 0 && blk < p.num_pages)
+                        src = reinterpret_cast<const uint4*>(kp + (((size_t)blk * p.G + kvh) * p.page + (key % p.page)) * D);
+                    else if (lane == 0 && p.err) atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
+                }
+                for (int c = lane; c < d8; c += 32)
+                    *reinterpret_cast<uint4*>(Ks + j * DP + c * 8) = src ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncthreads();
+
+            // S = Q K^T for the slab's 16 rows and the tile's 32 keys
+            float sc[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { sc[i][0] = 0.0f; sc[i][1] = 0.0f; sc[i][2] = 0.0f; sc[i][3] = 0.0f; }
+            const __nv_bfloat16* qa = Qs + (wr * 16 + (lane & 15)) * DP + (lane >> 4) * 8;
+            const __nv_bfloat16* kb = Ks + ((lane >> 4) * 8 + (lane & 7)) * DP + ((lane >> 3) & 1) * 8;
+            for (int kk = 0; kk < D; kk += 16) {
+                uint32_t af[4], b01[4], b23[4];
+                ldmatrix_x4(af, qa + kk);
+                ldmatrix_x4(b01, kb + kk);                      // keys 0..15: (b0, b1) of key tiles 0 and 1
+                ldmatrix_x4(b23, kb + 16 * DP + kk);            // keys 16..31
+                mma_bf16(sc[0], af, b01[0], b01[1]);
+                mma_bf16(sc[1], af, b01[2], b01[3]);
+                mma_bf16(sc[2], af, b23[0], b23[1]);
+                mma_bf16(sc[3], af, b23[2], b23[3]);
+            }
+            // mask, running maximum, weights
+            float tmA = -INFINITY, tmB = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int key = k0 + nt * 8 + 2 * t + e;
+                    const bool in = key >= a && key < b;
+                    const bool vA = liveA && in && key <= qposA && (p.window <= 0 || qposA - key < p.window || key < p.keep_first);
+                    const bool vB = liveB && in && key <= qposB && (p.window <= 0 || qposB - key < p.window || key < p.keep_first);
+                    sc[nt][e] = vA ? sc[nt][e] * p.scale : -INFINITY;
+                    sc[nt][2 + e] = vB ? sc[nt][2 + e] * p.scale : -INFINITY;
+                    tmA = fmaxf(tmA, sc[nt][e]);
+                    tmB = fmaxf(tmB, sc[nt][2 + e]);
+                }
+            tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 1)); tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 2));
+            tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 1)); tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 2));
+            const float nA = fmaxf(mA, tmA), nB = fmaxf(mB, tmB);
+            const float cA = nA == -INFINITY ? 1.0f : expf(mA - nA), cB = nB == -INFINITY ? 1.0f : expf(mB - nB);
+            float sA = 0.0f, sB = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const float pa = nA == -INFINITY ? 0.0f : expf(sc[nt][e] - nA);
+                    const float pb = nB == -INFINITY ? 0.0f : expf(sc[nt][2 + e] - nB);
+                    sc[nt][e] = pa; sc[nt][2 + e] = pb;
+                    sA += pa; sB += pb;
+                }
+            sA += __shfl_xor_sync(0xffffffffu, sA, 1); sA += __shfl_xor_sync(0xffffffffu, sA, 2);
+            sB += __shfl_xor_sync(0xffffffffu, sB, 1); sB += __shfl_xor_sync(0xffffffffu, sB, 2);
+            lA = lA * cA + sA; lB = lB * cB + sB;
+            mA = nA; mB = nB;
+#pragma unroll
+            for (int i = 0; i < NTO; i++) { o[i][0] *= cA; o[i][1] *= cA; o[i][2] *= cB; o[i][3] *= cB; }
+            // O += P V: the value of key j is the first DV elements of its row
+#pragma unroll
+            for (int ks = 0; ks < 2; ks++) {
+                uint32_t pf[4];
+                pf[0] = pack_bf16(sc[2 * ks][0], sc[2 * ks][1]);
+                pf[1] = pack_bf16(sc[2 * ks][2], sc[2 * ks][3]);
+                pf[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
+                pf[3] = pack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+                const __nv_bfloat16* vb = Ks + (ks * 16 + (lane & 15)) * DP + col0 + (lane >> 4) * 8;
+#pragma unroll
+                for (int i = 0; i < NTO; i += 2) {
+                    if (i * 8 < half) {                          // uniform
+                        uint32_t vf[4];
+                        ldmatrix_x4_trans(vf, vb + i * 8);       // value columns i * 8 .. + 15, keys ks * 16 .. + 15
+                        mma_bf16(o[i], pf, vf[0], vf[1]);
+                        if ((i + 1) * 8 < half) mma_bf16(o[i + 1], pf, vf[2], vf[3]);
+                    }
+                }
+            }
+        }
+    }
+
+    // the sink joins the denominator once; write the two rows' columns
+    float invA = 0.0f, invB = 0.0f;
+    {
+        const int hA = head0 + (liveA ? rA % nh : 0), hB = head0 + (liveB ? rB % nh : 0);
+        float mm = mA, ll = lA, corr = 1.0f;
+        if (p.sink) { const float sk = p.sink[hA]; mm = fmaxf(mA, sk); corr = mA == -INFINITY ? 0.0f : expf(mA - mm); ll = lA * corr + expf(sk - mm); }
+        invA = ll > 0.0f ? corr / ll : 0.0f;
+        mm = mB; ll = lB; corr = 1.0f;
+        if (p.sink) { const float sk = p.sink[hB]; mm = fmaxf(mB, sk); corr = mB == -INFINITY ? 0.0f : expf(mB - mm); ll = lB * corr + expf(sk - mm); }
+        invB = ll > 0.0f ? corr / ll : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < NTO; i++) {
+        const int c = i * 8 + 2 * t;
+        if (c >= half) continue;
+        if (liveA) {
+            TO* dst = (TO*)p.out + ((size_t)(row0 + rA / nh) * p.H + head0 + rA % nh) * DV + col0 + c;
+            dst[0] = from_float<TO>(o[i][0] * invA); dst[1] = from_float<TO>(o[i][1] * invA);
+        }
+        if (liveB) {
+            TO* dst = (TO*)p.out + ((size_t)(row0 + rB / nh) * p.H + head0 + rB % nh) * DV + col0 + c;
+            dst[0] = from_float<TO>(o[i][2] * invB); dst[1] = from_float<TO>(o[i][3] * invB);
+        }
+    }
+}
+
+template <typename TO>
+int launch_shared_row_tc(const SinkAttnParams& p, int n_tiles, cudaStream_t st) {
+    const size_t smem = (size_t)(LT_ROWS + LT_KT) * (p.D + LT_PAD) * sizeof(__nv_bfloat16);
+    if (smem > 220 * 1024) return fail("sink_attention: rows of %d need %zu bytes of shared memory", p.D, smem);
+    const int group = p.H / p.G, chunks = (group + p.head_chunk - 1) / p.head_chunk;
+    dim3 grid(n_tiles, p.G * chunks);
+    const int nto = (p.DV / 2 + 7) / 8;
+    auto run = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail("sink_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
+        launch_kernel(kernel, grid, 256, smem, st, p);
+        return check_launch("shared_row_attention_tc");
+    };
+    if (nto <= 4) return run(shared_row_attention_tc_kernel<TO, 4>);
+    if (nto <= 8) return run(shared_row_attention_tc_kernel<TO, 8>);
+    if (nto <= 16) return run(shared_row_attention_tc_kernel<TO, 16>);
+    return run(shared_row_attention_tc_kernel<TO, 32>);
+}
+
 }  // namespace ember
 
 using namespace ember;
@@ -610,4 +820,28 @@ EMBER_API int ember_sink_attention(const void* q, const void* k_pool, const void
         return out_f32 ? launch_sink_attention<__nv_bfloat16, float>(p, n_tiles, T_tokens, st)
                        : launch_sink_attention<__nv_bfloat16, __nv_bfloat16>(p, n_tiles, T_tokens, st);
     return fail("sink_attention: unsupported dtype %d", dtype);
+}
+
+// The tensor-core form for bfloat16 caches without a value pool (a value is the first DV elements of the key row):
+// D and DV multiples of 16, DV <= 512, tiles of 64 / heads-per-block query tokens, no splits.
+EMBER_API int ember_shared_row_attention_tc_head_chunk(int group) { return group <= 0 ? 0 : (group < LT_ROWS ? group : LT_ROWS); }
+
+EMBER_API int ember_shared_row_attention_tc(const void* q, const void* k_pool, void* out, int out_f32, int T_tokens, int H, int G, int D,
+                                            int DV, const int* tiles, int n_tiles, int tile_q, const int* block_table, int max_blocks,
+                                            int page, int num_pages, int window, int keep_first, const float* sink, float scale,
+                                            int* err, void* stream) {
+    if (n_tiles <= 0 || T_tokens <= 0) return 0;
+    if (D <= 0 || DV <= 0 || (D & 15) || (DV & 15) || DV > D || DV > 512) return fail("shared_row_attention_tc: rows of %d / %d are not taken", D, DV);
+    if (H <= 0 || G <= 0 || H % G) return fail("shared_row_attention_tc: %d heads do not divide into %d groups", H, G);
+    const int chunk = ember_shared_row_attention_tc_head_chunk(H / G);
+    if (tile_q <= 0 || tile_q * chunk > LT_ROWS) return fail("shared_row_attention_tc: tiles of %d queries x %d heads exceed %d rows", tile_q, chunk, LT_ROWS);
+    if ((long long)G * ((H / G + chunk - 1) / chunk) > 65535) return fail("shared_row_attention_tc: grid too large");
+    if (page <= 0 || max_blocks <= 0 || num_pages <= 0 || window < 0 || keep_first < 0) return fail("shared_row_attention_tc: bad cache geometry");
+    SinkAttnParams p;
+    p.q = q; p.k_pool = k_pool; p.v_pool = nullptr; p.out = out; p.part_o = nullptr; p.part_ml = nullptr;
+    p.tiles = tiles; p.block_table = block_table; p.sink = sink; p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages;
+    p.H = H; p.G = G; p.D = D; p.DV = DV; p.head_chunk = chunk; p.window = window; p.keep_first = keep_first; p.scale = scale;
+    p.n_splits = 1; p.split_keys = 0; p.err = err;
+    cudaStream_t st = (cudaStream_t)stream;
+    return out_f32 ? launch_shared_row_tc<float>(p, n_tiles, st) : launch_shared_row_tc<__nv_bfloat16>(p, n_tiles, st);
 }

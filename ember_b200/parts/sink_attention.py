@@ -40,7 +40,16 @@ class _SinkSoftmax(Mixer):
     SPLIT_KEYS = 256            # keys per split, and the most tokens in a step for which key ranges are split
     SPLIT_MAX_TOKENS = 64
 
+    TC_MIN_TOKENS = 65          # from here on a bfloat16 step over shared key/value rows takes the tensor cores
+
     def _attend(self, ctx, q, k_pool, v_pool, out, table, page, heads, kv_heads, dim, vdim, window, keep_first, sink, scale):
+        if ctx.T >= self.TC_MIN_TOKENS and ops.shared_row_attention_tc_usable(q, v_pool, dim, vdim):
+            # prompt portions over rows that serve as key and value: scores and the weighted sum on mma.sync
+            tile_q = ops.shared_row_attention_tc_tile_queries(heads // kv_heads)
+            tiles, n_tiles = ctx.attention_tiles(tile_q, "all")
+            ops.shared_row_attention_tc(q, k_pool, out, ctx.T, heads, kv_heads, dim, vdim, tiles, n_tiles, tile_q, table, page,
+                                        window, keep_first, sink, scale, err=ctx.err, stream=ctx.stream)
+            return
         tile_q = ops.sink_attention_tile_queries(heads // kv_heads)
         tiles, n_tiles = ctx.attention_tiles(tile_q, "all")
         span = ctx.max_context if window <= 0 else min(ctx.max_context, window + keep_first + tile_q)
@@ -180,7 +189,9 @@ class LatentAttention(_SinkSoftmax):
         return CacheNeed(kind="full", num_kv_heads=1, head_dim=self.row, keys_only=True)
 
     def tile_requests(self):
-        return [(ops.sink_attention_tile_queries(self.spec.num_heads), "all")]
+        keys = [(ops.sink_attention_tile_queries(self.spec.num_heads), "all")]
+        tc = (ops.shared_row_attention_tc_tile_queries(self.spec.num_heads), "all")
+        return keys + ([tc] if tc not in keys else [])
 
     def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
         s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens

@@ -284,6 +284,22 @@ def test_latent_attention_alone(dtype, heads, dim, rot_dim, vdim, q_rank, kv_ran
     assert _rel(_run_mixer(spec, w, x, dtype), _latent_plain(x, w, m)) < MIX_TOL[dtype]
 
 
+@pytest.mark.parametrize("heads,dim,rot_dim,vdim,q_rank,kv_rank,dims,base,hidden", [
+    (4, 128, 64, 128, 192, 256, 64, 1e6, 128), (16, 16, 16, 16, 32, 48, 16, 1e4, 64), (40, 8, 16, 8, 16, 32, 8, 77.0, 64),
+    (3, 24, 16, 20, 48, 64, 16, 500.0, 72)])
+def test_latent_attention_on_tensor_cores(heads, dim, rot_dim, vdim, q_rank, kv_rank, dims, base, hidden):
+    """bfloat16 portions of 65 tokens and more take the tensor-core kernel (rows and latents that are multiples of 16):
+    tiles of 64 (token, head) rows that are full, ragged (three heads: 63 rows) or one token of forty heads; a latent
+    whose halves are no multiple of 16 columns; decoded tokens beside the portions and after them."""
+    spec = _latent_spec(heads, dim, rot_dim, vdim, q_rank, kv_rank, dims, base, hidden)
+    w = _weights(spec, seed=heads, std=0.12)
+    x = torch.randn(200, hidden, generator=torch.Generator().manual_seed(8)).bfloat16()
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": 0.2,
+         "rot": {"dims": dims, "base": base}}
+    got = _run_mixer(spec, w, x, torch.bfloat16, portions=((100, 3), (30, 40), (68, 1), (1, 1), (1, 1)))
+    assert _rel(got, _latent_plain(x, w, m)) < MIX_TOL[torch.bfloat16]
+
+
 def test_a_far_rotated_key_that_dominates_is_seen_across_pages_and_portions():
     """Scores that rest on the rotated key part alone (the unrotated queries are zero): a far key whose rotated part
     is large, queries that match it only if both were turned by their own positions' angles."""
