@@ -513,12 +513,13 @@ int launch_sink_attention(const SinkAttnParams& p, int n_tiles, int T_tokens, cu
 
 
 // ------------------------------------------------- attention over shared key rows on the tensor cores (bfloat16)
-// For the layout in which one cached row serves every query head as key and, with its first DV elements, as value
-// (no value pool).  A block takes 64 (query, head) rows and walks the visible keys 32 at a time: scores
+// Keys and values from their pools, or (no value pool) one cached row that serves every query head as key and, with
+// its first DV elements, as value.  A block takes 64 (query, head) rows and walks the visible keys 32 at a time: scores
 // S = Q K^T and O += P V on mma.sync m16n8k16 (bf16 operands, fp32 accumulators), the softmax with its running maximum,
 // denominators and the sink in fp32 registers.  Eight warps: warp (wr, wc) owns rows 16 wr .. 16 wr + 15 and the
 // half wc of the value columns; both warps of a row slab compute the slab's scores (the same numbers), so no
-// exchange is needed.  P enters the second product rounded to bfloat16, as V is.
+// exchange is needed.  P enters the second product rounded to bfloat16, as V is.  Key tiles arrive by cp.async into
+// two buffers, one tile ahead; with key splits a block leaves partial sums for the merge kernel, like the general form.
 constexpr int LT_ROWS = 64, LT_KT = 32, LT_PAD = 8;
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
@@ -545,8 +546,14 @@ __global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAtt
     pdl_launch_dependents();
     pdl_wait();
     const int D = p.D, DV = p.DV, DP = D + LT_PAD;
+    const int VP = DV + LT_PAD;
+    const bool alias = p.v_pool == nullptr;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][DP]
-    __nv_bfloat16* Ks = Qs + LT_ROWS * DP;                                      // [32][DP]
+    __nv_bfloat16* Kb = Qs + LT_ROWS * DP;                                      // 2 x [32][DP]
+    __nv_bfloat16* Vb = alias ? Kb : Kb + 2 * LT_KT * DP;                       // 2 x [32][VP], or the key rows themselves
+    const int v_ld = alias ? DP : VP;
+    const __nv_bfloat16* vp = (const __nv_bfloat16*)p.v_pool;
+    const int v8 = DV / 8;
     const int group = p.H / p.G;
     const int chunks = (group + p.head_chunk - 1) / p.head_chunk;
     const int tile = blockIdx.x, kvh = blockIdx.y / chunks, hc = blockIdx.y - kvh * chunks;
@@ -584,24 +591,69 @@ __global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAtt
     for (int i = 0; i < NTO; i++) { o[i][0] = 0.0f; o[i][1] = 0.0f; o[i][2] = 0.0f; o[i][3] = 0.0f; }
 
     const int* bt = p.block_table + (size_t)seq * p.max_blocks;
-    for (int part = 0; part < 2; part++) {
-        const int a = part == 0 ? 0 : lo, b = part == 0 ? kept : hi;
-        if (a >= b) continue;
-        for (int k0 = a - (a % LT_KT); k0 < b; k0 += LT_KT) {
-            __syncthreads();
-            for (int j = warp; j < LT_KT; j += 8) {
-                const int key = k0 + j;
-                const uint4* src = nullptr;
-                if (key >= a && key < b) {
-                    const int blk = bt[key / p.page];
-                    if (blk >= 0 && blk < p.num_pages)
-                        src = reinterpret_cast<const uint4*>(kp + (((size_t)blk * p.G + kvh) * p.page + (key % p.page)) * D);
-                    else if (lane == 0 && p.err) atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
-                }
-                for (int c = lane; c < d8; c += 32)
-                    *reinterpret_cast<uint4*>(Ks + j * DP + c * 8) = src ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+    // the key tiles of the two visible ranges ([0, kept) and [lo, hi), inside this block's split), one after the other;
+    // tile i + 1 is on its way into the other buffer (cp.async) while tile i is computed
+    int s_lo = 0, s_hi = hi;
+    if (p.n_splits > 1) { s_lo = blockIdx.z * p.split_keys; s_hi = min(hi, (int)(blockIdx.z + 1) * p.split_keys); }
+    const int a0 = max(0, s_lo), b0 = min(kept, s_hi), a1 = max(lo, s_lo), b1 = min(hi, s_hi);
+    const int f0 = a0 - (a0 % LT_KT), f1 = a1 - (a1 % LT_KT);
+    const int n0 = a0 < b0 ? (b0 - f0 + LT_KT - 1) / LT_KT : 0, n1 = a1 < b1 ? (b1 - f1 + LT_KT - 1) / LT_KT : 0;
+    const int n_key_tiles = n0 + n1;
+    auto issue = [&](int i) {
+        const int k0 = i < n0 ? f0 + i * LT_KT : f1 + (i - n0) * LT_KT;
+        const int a = i < n0 ? a0 : a1, b = i < n0 ? b0 : b1;
+        __nv_bfloat16* Ks = Kb + (i & 1) * LT_KT * DP;
+        __nv_bfloat16* Vs = alias ? Ks : Vb + (i & 1) * LT_KT * VP;
+        long long rowi[LT_KT / 8];
+#pragma unroll
+        for (int u = 0; u < LT_KT / 8; u++) {                  // the warp's rows: all look-ups first
+            const int key = k0 + warp + 8 * u;
+            rowi[u] = -1;
+            if (key >= a && key < b) {
+                const int blk = bt[key / p.page];
+                if (blk >= 0 && blk < p.num_pages) rowi[u] = ((long long)blk * p.G + kvh) * p.page + (key % p.page);
+                else if (lane == 0 && p.err) atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
             }
-            __syncthreads();
+        }
+#pragma unroll
+        for (int u = 0; u < LT_KT / 8; u++) {
+            const int j = warp + 8 * u;
+            for (int c = lane; c < d8; c += 32) {
+                __nv_bfloat16* dst = Ks + j * DP + c * 8;
+                if (rowi[u] >= 0) {
+                    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(kp + rowi[u] * D + c * 8) : "memory");
+                } else {
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            if (!alias)
+                for (int c = lane; c < v8; c += 32) {
+                    __nv_bfloat16* dst = Vs + j * VP + c * 8;
+                    if (rowi[u] >= 0) {
+                        const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst);
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(vp + rowi[u] * DV + c * 8) : "memory");
+                    } else {
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (n_key_tiles > 0) issue(0);
+    {
+        for (int it = 0; it < n_key_tiles; it++) {
+            if (it + 1 < n_key_tiles) {
+                issue(it + 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();                                    // tile `it` has landed (and, the first time, the queries)
+            const int k0 = it < n0 ? f0 + it * LT_KT : f1 + (it - n0) * LT_KT;
+            const int a = it < n0 ? a0 : a1, b = it < n0 ? b0 : b1;
+            const __nv_bfloat16* Ks = Kb + (it & 1) * LT_KT * DP;
+            const __nv_bfloat16* Vs = alias ? Ks : Vb + (it & 1) * LT_KT * VP;
 
             // S = Q K^T for the slab's 16 rows and the tile's 32 keys
             float sc[4][4];
@@ -662,7 +714,7 @@ __global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAtt
                 pf[1] = pack_bf16(sc[2 * ks][2], sc[2 * ks][3]);
                 pf[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
                 pf[3] = pack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
-                const __nv_bfloat16* vb = Ks + (ks * 16 + (lane & 15)) * DP + col0 + (lane >> 4) * 8;
+                const __nv_bfloat16* vb = Vs + (ks * 16 + (lane & 15)) * v_ld + col0 + (lane >> 4) * 8;
 #pragma unroll
                 for (int i = 0; i < NTO; i += 2) {
                     if (i * 8 < half) {                          // uniform
@@ -673,7 +725,36 @@ __global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAtt
                     }
                 }
             }
+            __syncthreads();                                    // the buffer is free for the tile after next
         }
+    }
+
+    if (p.n_splits > 1) {
+        // a split leaves its sums, maximum and denominator; the merge kernel adds the sink
+#pragma unroll
+        for (int i = 0; i < NTO; i++) {
+            const int c = i * 8 + 2 * t;
+            if (c >= half) continue;
+            if (liveA) {
+                float* dst = p.part_o + ((((size_t)(row0 + rA / nh) * p.H + head0 + rA % nh) * p.n_splits) + blockIdx.z) * DV + col0 + c;
+                dst[0] = o[i][0]; dst[1] = o[i][1];
+            }
+            if (liveB) {
+                float* dst = p.part_o + ((((size_t)(row0 + rB / nh) * p.H + head0 + rB % nh) * p.n_splits) + blockIdx.z) * DV + col0 + c;
+                dst[0] = o[i][2]; dst[1] = o[i][3];
+            }
+        }
+        if (wc == 0 && t == 0) {
+            if (liveA) {
+                float* ml = p.part_ml + ((((size_t)(row0 + rA / nh) * p.H + head0 + rA % nh) * p.n_splits) + blockIdx.z) * 2;
+                ml[0] = mA; ml[1] = lA;
+            }
+            if (liveB) {
+                float* ml = p.part_ml + ((((size_t)(row0 + rB / nh) * p.H + head0 + rB % nh) * p.n_splits) + blockIdx.z) * 2;
+                ml[0] = mB; ml[1] = lB;
+            }
+        }
+        return;
     }
 
     // the sink joins the denominator once; write the two rows' columns
@@ -703,11 +784,11 @@ __global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAtt
 }
 
 template <typename TO>
-int launch_shared_row_tc(const SinkAttnParams& p, int n_tiles, cudaStream_t st) {
-    const size_t smem = (size_t)(LT_ROWS + LT_KT) * (p.D + LT_PAD) * sizeof(__nv_bfloat16);
+int launch_shared_row_tc(const SinkAttnParams& p, int n_tiles, int T_tokens, cudaStream_t st) {
+    const size_t smem = ((size_t)(LT_ROWS + 2 * LT_KT) * (p.D + LT_PAD) + (p.v_pool ? (size_t)2 * LT_KT * (p.DV + LT_PAD) : 0)) * sizeof(__nv_bfloat16);
     if (smem > 220 * 1024) return fail("sink_attention: rows of %d need %zu bytes of shared memory", p.D, smem);
     const int group = p.H / p.G, chunks = (group + p.head_chunk - 1) / p.head_chunk;
-    dim3 grid(n_tiles, p.G * chunks);
+    dim3 grid(n_tiles, p.G * chunks, p.n_splits);
     const int nto = (p.DV / 2 + 7) / 8;
     auto run = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -715,10 +796,18 @@ int launch_shared_row_tc(const SinkAttnParams& p, int n_tiles, cudaStream_t st) 
         launch_kernel(kernel, grid, 256, smem, st, p);
         return check_launch("shared_row_attention_tc");
     };
-    if (nto <= 4) return run(shared_row_attention_tc_kernel<TO, 4>);
-    if (nto <= 8) return run(shared_row_attention_tc_kernel<TO, 8>);
-    if (nto <= 16) return run(shared_row_attention_tc_kernel<TO, 16>);
-    return run(shared_row_attention_tc_kernel<TO, 32>);
+    int rc;
+    if (nto <= 4) rc = run(shared_row_attention_tc_kernel<TO, 4>);
+    else if (nto <= 8) rc = run(shared_row_attention_tc_kernel<TO, 8>);
+    else if (nto <= 16) rc = run(shared_row_attention_tc_kernel<TO, 16>);
+    else rc = run(shared_row_attention_tc_kernel<TO, 32>);
+    if (rc) return rc;
+    if (p.n_splits > 1) {
+        launch_kernel(sink_combine_kernel<TO>, (unsigned)((size_t)T_tokens * p.H), p.DV >= 128 ? 128 : 64, 0, st,
+                      (const float*)p.part_o, (const float*)p.part_ml, p.sink, (TO*)p.out, p.n_splits, p.DV, p.H);
+        return check_launch("sink_combine");
+    }
+    return 0;
 }
 
 }  // namespace ember
@@ -822,26 +911,29 @@ EMBER_API int ember_sink_attention(const void* q, const void* k_pool, const void
     return fail("sink_attention: unsupported dtype %d", dtype);
 }
 
-// The tensor-core form for bfloat16 caches without a value pool (a value is the first DV elements of the key row):
-// D and DV multiples of 16, DV <= 512, tiles of 64 / heads-per-block query tokens, no splits.
+// The tensor-core form for bfloat16 caches, with a value pool or without (a value is then the first DV elements of
+// the key row): D and DV multiples of 16, DV <= 512, tiles of 64 / heads-per-block query tokens; key splits as in
+// ember_sink_attention.
 EMBER_API int ember_shared_row_attention_tc_head_chunk(int group) { return group <= 0 ? 0 : (group < LT_ROWS ? group : LT_ROWS); }
 
-EMBER_API int ember_shared_row_attention_tc(const void* q, const void* k_pool, void* out, int out_f32, int T_tokens, int H, int G, int D,
+EMBER_API int ember_shared_row_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out, int out_f32, int T_tokens, int H, int G, int D,
                                             int DV, const int* tiles, int n_tiles, int tile_q, const int* block_table, int max_blocks,
                                             int page, int num_pages, int window, int keep_first, const float* sink, float scale,
-                                            int* err, void* stream) {
+                                            int n_splits, int split_keys, float* part_o, float* part_ml, int* err, void* stream) {
     if (n_tiles <= 0 || T_tokens <= 0) return 0;
-    if (D <= 0 || DV <= 0 || (D & 15) || (DV & 15) || DV > D || DV > 512) return fail("shared_row_attention_tc: rows of %d / %d are not taken", D, DV);
+    if (D <= 0 || DV <= 0 || (D & 15) || (DV & 15) || (!v_pool && DV > D) || DV > 512) return fail("shared_row_attention_tc: rows of %d / %d are not taken", D, DV);
     if (H <= 0 || G <= 0 || H % G) return fail("shared_row_attention_tc: %d heads do not divide into %d groups", H, G);
     const int chunk = ember_shared_row_attention_tc_head_chunk(H / G);
     if (tile_q <= 0 || tile_q * chunk > LT_ROWS) return fail("shared_row_attention_tc: tiles of %d queries x %d heads exceed %d rows", tile_q, chunk, LT_ROWS);
-    if ((long long)G * ((H / G + chunk - 1) / chunk) > 65535) return fail("shared_row_attention_tc: grid too large");
+    if ((long long)G * ((H / G + chunk - 1) / chunk) > 65535 || n_splits > 65535) return fail("shared_row_attention_tc: grid too large");
+    if (n_splits < 1 || (n_splits > 1 && (split_keys <= 0 || !part_o || !part_ml)))
+        return fail("shared_row_attention_tc: bad split configuration (%d splits of %d keys)", n_splits, split_keys);
     if (page <= 0 || max_blocks <= 0 || num_pages <= 0 || window < 0 || keep_first < 0) return fail("shared_row_attention_tc: bad cache geometry");
     SinkAttnParams p;
-    p.q = q; p.k_pool = k_pool; p.v_pool = nullptr; p.out = out; p.part_o = nullptr; p.part_ml = nullptr;
+    p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.out = out; p.part_o = part_o; p.part_ml = part_ml;
     p.tiles = tiles; p.block_table = block_table; p.sink = sink; p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages;
     p.H = H; p.G = G; p.D = D; p.DV = DV; p.head_chunk = chunk; p.window = window; p.keep_first = keep_first; p.scale = scale;
-    p.n_splits = 1; p.split_keys = 0; p.err = err;
+    p.n_splits = n_splits; p.split_keys = split_keys; p.err = err;
     cudaStream_t st = (cudaStream_t)stream;
-    return out_f32 ? launch_shared_row_tc<float>(p, n_tiles, st) : launch_shared_row_tc<__nv_bfloat16>(p, n_tiles, st);
+    return out_f32 ? launch_shared_row_tc<float>(p, n_tiles, T_tokens, st) : launch_shared_row_tc<__nv_bfloat16>(p, n_tiles, T_tokens, st);
 }

@@ -1112,23 +1112,27 @@ SHARED_ROW_TC_ROWS = 64          # (query, head) rows of a block of the tensor-c
 
 
 def shared_row_attention_tc_usable(q: torch.Tensor, v_pool, dim: int, vdim: int) -> bool:
-    """Whether the tensor-core form of ``sink_attention`` takes this layout: bfloat16, no value pool (a value is the
-    first ``vdim`` elements of the key row), sizes that are multiples of 16."""
-    return (TC_ENABLED and q.dtype == torch.bfloat16 and v_pool is None and dim % 16 == 0 and vdim % 16 == 0 and vdim <= min(dim, 512)
-            and (SHARED_ROW_TC_ROWS + 32) * (dim + 8) * 2 <= 220 * 1024)
+    """Whether the tensor-core form of ``sink_attention`` takes this layout: bfloat16, head sizes that are multiples
+    of 16 (with or without a value pool)."""
+    return (TC_ENABLED and q.dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and vdim <= 512
+            and (v_pool is not None or vdim <= dim)
+            and ((SHARED_ROW_TC_ROWS + 64) * (dim + 8) + (64 * (vdim + 8) if v_pool is not None else 0)) * 2 <= 220 * 1024)
 
 
 def shared_row_attention_tc_tile_queries(group: int) -> int:
     return max(1, SHARED_ROW_TC_ROWS // max(1, min(group, SHARED_ROW_TC_ROWS)))
 
 
-def shared_row_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, out: torch.Tensor, T: int, heads: int, kv_heads: int, dim: int,
+def shared_row_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch.Tensor], out: torch.Tensor, T: int, heads: int, kv_heads: int, dim: int,
                             vdim: int, tiles: torch.Tensor, n_tiles: int, tile_q: int, block_table: torch.Tensor, page: int,
-                            window: int, keep_first: int, sink: Optional[torch.Tensor], scale: float,
+                            window: int, keep_first: int, sink: Optional[torch.Tensor], scale: float, n_splits: int = 1,
+                            split_keys: int = 0, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
                             err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
-    """``sink_attention`` without a value pool on the tensor cores (bfloat16 rows; scores, weights and sums fp32)."""
+    """``sink_attention`` on the tensor cores (bfloat16 queries, keys, values; scores, weights and sums fp32)."""
     _check(q, "q", torch.bfloat16)
     _check(k_pool, "k_pool", torch.bfloat16)
+    if v_pool is not None:
+        _check(v_pool, "v_pool", torch.bfloat16)
     _check(out, "out")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"shared_row_attention_tc: output {out.dtype}")
@@ -1138,11 +1142,16 @@ def shared_row_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, out: torch.Te
         _check(sink, "sink", torch.float32)
         if sink.numel() != heads:
             raise KernelError(f"shared_row_attention_tc: {sink.numel()} sinks for {heads} heads")
-    _check_pages(k_pool, None, kv_heads, page, dim, vdim, "shared_row_attention_tc")
+    _check_pages(k_pool, v_pool, kv_heads, page, dim, vdim, "shared_row_attention_tc")
     if q.numel() < T * heads * dim or out.numel() < T * heads * vdim:
         raise KernelError("shared_row_attention_tc: q/out too small for the step")
+    if n_splits > 1:
+        _check(part_o, "part_o", torch.float32)
+        _check(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < T * heads * n_splits * vdim or part_ml.numel() < T * heads * n_splits * 2:
+            raise KernelError("shared_row_attention_tc: split buffers too small")
     lib = _lib("sink_attention")
-    _call(lib, lib.ember_shared_row_attention_tc, _p(q), _p(k_pool), _p(out), c_int(1 if out.dtype == torch.float32 else 0), c_int(T),
+    _call(lib, lib.ember_shared_row_attention_tc, _p(q), _p(k_pool), _p(v_pool), _p(out), c_int(1 if out.dtype == torch.float32 else 0), c_int(T),
           c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), _p(tiles), c_int(n_tiles), c_int(tile_q), _p(block_table),
           c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), c_int(window), c_int(keep_first), _p(sink),
-          c_float(scale), _p(err), _stream(stream))
+          c_float(scale), c_int(n_splits), c_int(split_keys), _p(part_o), _p(part_ml), _p(err), _stream(stream))

@@ -40,27 +40,30 @@ class _SinkSoftmax(Mixer):
     SPLIT_KEYS = 256            # keys per split, and the most tokens in a step for which key ranges are split
     SPLIT_MAX_TOKENS = 64
 
-    TC_MIN_TOKENS = 65          # from here on a bfloat16 step over shared key/value rows takes the tensor cores
+    # From how many tokens on a bfloat16 step takes the tensor-core kernel.  Measured at 16 heads over latent rows of 576
+    # and 16/8 heads of 128 (eight layers, context 1,024): a decode step at batch 8 takes 2.20 ms with it against 2.95 ms
+    # with the general kernel, at batch 64 4.93 against 6.14 ms; tests set it higher to run the general kernel in bfloat16.
+    TC_MIN_TOKENS = int(__import__("os").environ.get("EMBER_SINK_TC_MIN_TOKENS", "1"))
 
     def _attend(self, ctx, q, k_pool, v_pool, out, table, page, heads, kv_heads, dim, vdim, window, keep_first, sink, scale):
-        if ctx.T >= self.TC_MIN_TOKENS and ops.shared_row_attention_tc_usable(q, v_pool, dim, vdim):
-            # prompt portions over rows that serve as key and value: scores and the weighted sum on mma.sync
-            tile_q = ops.shared_row_attention_tc_tile_queries(heads // kv_heads)
-            tiles, n_tiles = ctx.attention_tiles(tile_q, "all")
-            ops.shared_row_attention_tc(q, k_pool, out, ctx.T, heads, kv_heads, dim, vdim, tiles, n_tiles, tile_q, table, page,
-                                        window, keep_first, sink, scale, err=ctx.err, stream=ctx.stream)
-            return
-        tile_q = ops.sink_attention_tile_queries(heads // kv_heads)
+        on_tc = ctx.T >= self.TC_MIN_TOKENS and ops.shared_row_attention_tc_usable(q, v_pool, dim, vdim)
+        tile_q = (ops.shared_row_attention_tc_tile_queries if on_tc else ops.sink_attention_tile_queries)(heads // kv_heads)
         tiles, n_tiles = ctx.attention_tiles(tile_q, "all")
+        # long key ranges of a small step are cut into fixed splits so that more SMs share them
         span = ctx.max_context if window <= 0 else min(ctx.max_context, window + keep_first + tile_q)
         n_splits, part_o, part_ml = 1, None, None
         if ctx.T <= self.SPLIT_MAX_TOKENS and span > 2 * self.SPLIT_KEYS:
             n_splits = (ctx.max_context + self.SPLIT_KEYS - 1) // self.SPLIT_KEYS
             part_o = ctx.buf_dyn("sink_attention.part_o", ctx.T * heads * n_splits * vdim, torch.float32)
             part_ml = ctx.buf_dyn("sink_attention.part_ml", ctx.T * heads * n_splits * 2, torch.float32)
-        ops.sink_attention(q, k_pool, v_pool, out, ctx.T, heads, kv_heads, dim, vdim, tiles, n_tiles, tile_q, table, page,
-                           window, keep_first, sink, scale, n_splits, self.SPLIT_KEYS, part_o, part_ml, err=ctx.err,
-                           stream=ctx.stream)
+        if on_tc:           # scores and the weighted sum on mma.sync
+            ops.shared_row_attention_tc(q, k_pool, v_pool, out, ctx.T, heads, kv_heads, dim, vdim, tiles, n_tiles, tile_q, table,
+                                        page, window, keep_first, sink, scale, n_splits, self.SPLIT_KEYS, part_o, part_ml,
+                                        err=ctx.err, stream=ctx.stream)
+        else:
+            ops.sink_attention(q, k_pool, v_pool, out, ctx.T, heads, kv_heads, dim, vdim, tiles, n_tiles, tile_q, table, page,
+                               window, keep_first, sink, scale, n_splits, self.SPLIT_KEYS, part_o, part_ml, err=ctx.err,
+                               stream=ctx.stream)
 
 
 class SinkAttention(_SinkSoftmax):
@@ -112,7 +115,10 @@ class SinkAttention(_SinkSoftmax):
                          keep_first=s.keep_first if s.window > 0 else 0)
 
     def tile_requests(self):
-        return [(ops.sink_attention_tile_queries(self.spec.num_heads // self.spec.num_kv_heads), "all")]
+        group = self.spec.num_heads // self.spec.num_kv_heads
+        keys = [(ops.sink_attention_tile_queries(group), "all")]
+        tc = (ops.shared_row_attention_tc_tile_queries(group), "all")
+        return keys + ([tc] if tc not in keys else [])
 
     def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
         s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens

@@ -175,11 +175,18 @@ def _sink_m(heads, kv, dim, vdim, window, keep, scale=0.2):
     return m
 
 
+@pytest.fixture(params=[1, 1 << 30], ids=["tensor-core attention", "general attention"])
+def attention_kernel(request, monkeypatch):
+    """bfloat16 steps take the tensor-core attention where the sizes allow; the second run keeps them on the general one."""
+    from ember_b200.parts.sink_attention import _SinkSoftmax
+    monkeypatch.setattr(_SinkSoftmax, "TC_MIN_TOKENS", request.param)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv,dim,vdim,window,keep,hidden", [(6, 2, 16, 24, 20, 3, 64), (4, 1, 20, 12, 7, 9, 100),
                                                                   (2, 2, 128, 128, 64, 1, 128), (3, 3, 18, 300, 1, 0, 72),
                                                                   (40, 1, 8, 8, 16, 16, 64), (2, 1, 32, 32, 0, 0, 64)])
-def test_sink_attention_alone(dtype, heads, kv, dim, vdim, window, keep, hidden):
+def test_sink_attention_alone(dtype, heads, kv, dim, vdim, window, keep, hidden, attention_kernel):
     """Biases, the norm over the whole projections, windows of one key up to none at all, more kept tokens than the
     window is long, values wider and narrower than keys, forty query heads on one key head."""
     spec = _sink_spec(heads, kv, dim, vdim, window, keep, hidden)
@@ -189,6 +196,42 @@ def test_sink_attention_alone(dtype, heads, kv, dim, vdim, window, keep, hidden)
     x = torch.randn(90, hidden, generator=torch.Generator().manual_seed(5)).bfloat16()
     want = plain.windowed_sink_attention(x.double(), {k: v.double() for k, v in w.items()}, "m.", _sink_m(heads, kv, dim, vdim, window, keep), 1e-6)
     assert _rel(_run_mixer(spec, w, x, dtype), want) < MIX_TOL[dtype]
+
+
+@pytest.mark.parametrize("heads,kv,dim,vdim,window,keep,hidden", [(4, 2, 128, 128, 64, 4, 128), (6, 2, 16, 32, 20, 3, 64),
+                                                                  (3, 1, 48, 16, 33, 40, 72), (40, 1, 16, 16, 7, 0, 64)])
+def test_sink_attention_on_tensor_cores(heads, kv, dim, vdim, window, keep, hidden):
+    """bfloat16 portions of 65 tokens and more of the windowed layers (head sizes that are multiples of 16): keys and
+    values from pools of their own, windows whose edges fall inside 32-key tiles, kept first tokens."""
+    spec = _sink_spec(heads, kv, dim, vdim, window, keep, hidden)
+    w = _weights(spec, seed=heads)
+    x = torch.randn(200, hidden, generator=torch.Generator().manual_seed(5)).bfloat16()
+    want = plain.windowed_sink_attention(x.double(), {k: v.double() for k, v in w.items()}, "m.", _sink_m(heads, kv, dim, vdim, window, keep), 1e-6)
+    got = _run_mixer(spec, w, x, torch.bfloat16, portions=((100, 3), (30, 40), (68, 1), (1, 1), (1, 1)))
+    assert _rel(got, want) < MIX_TOL[torch.bfloat16]
+
+
+@pytest.mark.parametrize("kind", ["latent", "windowed", "whole"])
+def test_tensor_core_attention_with_key_splits(kind, monkeypatch):
+    """Small bfloat16 steps through the tensor-core kernel with their key ranges cut into splits of 32 keys that a
+    second kernel merges (the sink joins there): latent rows, a windowed layer whose early splits are empty but for the
+    kept tokens, and a layer that sees everything."""
+    from ember_b200.parts.sink_attention import _SinkSoftmax
+    monkeypatch.setattr(_SinkSoftmax, "TC_MIN_TOKENS", 1)
+    monkeypatch.setattr(_SinkSoftmax, "SPLIT_KEYS", 32)
+    x = torch.randn(200, 64, generator=torch.Generator().manual_seed(5)).bfloat16()
+    portions = ((150, 3), (20, 10), (28, 1), (1, 1), (1, 1))
+    if kind == "latent":
+        spec = _latent_spec(4, 16, 16, 16, 32, 48, 16, 1e4, 64)
+        w = _weights(spec, seed=4, std=0.12)
+        want = _latent_plain(x, w, {"heads": 4, "dim": 16, "rot_dim": 16, "vdim": 16, "q_rank": 32, "kv_rank": 48, "scale": 0.2,
+                                    "rot": {"dims": 16, "base": 1e4}})
+    else:
+        window, keep = (40, 5) if kind == "windowed" else (0, 0)
+        spec = _sink_spec(4, 2, 32, 16, window, keep, 64)
+        w = _weights(spec, seed=4)
+        want = plain.windowed_sink_attention(x.double(), {k: v.double() for k, v in w.items()}, "m.", _sink_m(4, 2, 32, 16, window, keep), 1e-6)
+    assert _rel(_run_mixer(spec, w, x, torch.bfloat16, portions=portions), want) < MIX_TOL[torch.bfloat16]
 
 
 def _one_hot_attention(window, keep, hidden=64, dim=32, vdim=48, heads=2):
@@ -273,7 +316,7 @@ def _latent_plain(x, w, m):
 @pytest.mark.parametrize("heads,dim,rot_dim,vdim,q_rank,kv_rank,dims,base,hidden", [
     (3, 24, 8, 20, 48, 40, 8, 1e4, 64), (2, 32, 16, 48, 24, 72, 8, 500.0, 100), (40, 8, 4, 6, 16, 20, 4, 77.0, 64),
     (4, 128, 64, 128, 192, 256, 64, 1e6, 128), (1, 16, 2, 16, 8, 512, 2, 10.0, 72)])
-def test_latent_attention_alone(dtype, heads, dim, rot_dim, vdim, q_rank, kv_rank, dims, base, hidden):
+def test_latent_attention_alone(dtype, heads, dim, rot_dim, vdim, q_rank, kv_rank, dims, base, hidden, attention_kernel):
     """The cached latent with the up-projections folded around the attention against keys and values built per head:
     a rotation over a part of the rotated part, forty heads on one latent, the widest latent, a single head."""
     spec = _latent_spec(heads, dim, rot_dim, vdim, q_rank, kv_rank, dims, base, hidden)
