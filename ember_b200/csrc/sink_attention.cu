@@ -7,7 +7,7 @@
 //   * rotate_pairs:      rotation of neighbouring pairs (2i, 2i + 1) of a slice of every head, fp32 in, cache type out;
 //   * head_gemm:         out[t, h, :] = W[h] x[t, h, :] for every head (a product per head, weights [H, N, K]), with an
 //     optional sigmoid gate on the result: folds a head's key up-projection into its query and takes a head's value
-//     up-projection of the attended latent;
+//     up-projection of the attended latent; fp32 multiply-adds in general, mma.sync tiles for bfloat16 weights;
 //   * sink_attention:    o = sum_j w_j v_j with w = softmax over the visible keys and one more term exp(sink[h]) in the
 //     denominator that has no key and no value; visible: j <= i and (no window, or i - j < window, or j < keep_first).
 //     Keys have D elements, values DV; with no value pool a value is the first DV elements of the key row (the
@@ -235,6 +235,12 @@ __global__ void __launch_bounds__(256) head_gemm_kernel(HeadGemmArgs p) {
             ((TO*)p.out)[(size_t)t * p.ld_o + (size_t)h * p.o_head + p.o_col + n] = from_float<TO>(v);
         }
     }
+}
+
+inline bool head_gemm_on_tensor_cores() {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("EMBER_HEAD_GEMM_TC"); on = (e && e[0] == '0') ? 0 : 1; }
+    return on != 0;
 }
 
 // ----------------------------------------------------------------------------------------------- attention
@@ -537,6 +543,66 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// The per-head product on the tensor cores: tiles of 64 tokens x 64 outputs, K in steps of 32, four warps of 16 rows; x is
+// rounded to bfloat16 as it enters shared memory (the weights are bfloat16), sums are fp32.
+constexpr int HT_BM = 64, HT_BN = 64, HT_BK = 32, HT_LD = HT_BK + 8;
+
+template <typename TO>
+__global__ void __launch_bounds__(128) head_gemm_tc_kernel(HeadGemmArgs p) {
+    __shared__ __align__(16) __nv_bfloat16 As[HT_BM * HT_LD];
+    __shared__ __align__(16) __nv_bfloat16 Bs[HT_BN * HT_LD];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.z, m0 = blockIdx.x * HT_BM, n0 = blockIdx.y * HT_BN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const __nv_bfloat16* w = (const __nv_bfloat16*)p.w + (size_t)h * p.N * p.K;
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
+    for (int k0 = 0; k0 < p.K; k0 += HT_BK) {
+        for (int idx = threadIdx.x; idx < HT_BM * (HT_BK / 4); idx += 128) {
+            const int r = idx / (HT_BK / 4), c = (idx - r * (HT_BK / 4)) * 4;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (m0 + r < p.T && k0 + c < p.K)
+                v = *reinterpret_cast<const float4*>(p.x + (size_t)(m0 + r) * p.ld_x + (size_t)h * p.x_head + p.x_col + k0 + c);
+            uint2 packed;
+            packed.x = pack_bf16(v.x, v.y);
+            packed.y = pack_bf16(v.z, v.w);
+            *reinterpret_cast<uint2*>(As + r * HT_LD + c) = packed;
+        }
+        for (int idx = threadIdx.x; idx < HT_BN * (HT_BK / 8); idx += 128) {
+            const int r = idx / (HT_BK / 8), c = (idx - r * (HT_BK / 8)) * 8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (n0 + r < p.N && k0 + c < p.K) v = *reinterpret_cast<const uint4*>(w + (size_t)(n0 + r) * p.K + k0 + c);
+            *reinterpret_cast<uint4*>(Bs + r * HT_LD + c) = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HT_BK; kk += 16) {
+            uint32_t af[4];
+            ldmatrix_x4(af, As + (warp * 16 + (lane & 15)) * HT_LD + kk + (lane >> 4) * 8);
+#pragma unroll
+            for (int nt = 0; nt < 8; nt += 2) {
+                uint32_t bf[4];
+                ldmatrix_x4(bf, Bs + ((nt + (lane >> 4)) * 8 + (lane & 7)) * HT_LD + kk + ((lane >> 3) & 1) * 8);
+                mma_bf16(acc[nt], af, bf[0], bf[1]);
+                mma_bf16(acc[nt + 1], af, bf[2], bf[3]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int row = m0 + warp * 16 + g + (e >> 1) * 8, n = n0 + nt * 8 + 2 * t + (e & 1);
+            if (row >= p.T || n >= p.N) continue;
+            float v = acc[nt][e];
+            if (p.gate) v *= sigmoidf_(p.gate[(size_t)row * p.ld_g + p.g_col + (size_t)h * p.N + n]);
+            ((TO*)p.out)[(size_t)row * p.ld_o + (size_t)h * p.o_head + p.o_col + n] = from_float<TO>(v);
+        }
 }
 
 // NTO: value-column tiles of 8 a warp owns (DV / 2 <= 8 NTO).
@@ -871,8 +937,15 @@ EMBER_API int ember_head_gemm(const float* x, int ld_x, int x_head, int x_col, c
     if (T <= 0) return 0;
     if (H <= 0 || N <= 0 || K <= 0 || H > 65535) return fail("head_gemm: %d heads of %d x %d", H, N, K);
     HeadGemmArgs p{x, ld_x, x_head, x_col, w, out, ld_o, o_head, o_col, gate, ld_g, g_col, T, H, N, K};
-    dim3 grid((T + HG_BM - 1) / HG_BM, (N + HG_BN - 1) / HG_BN, H);
     cudaStream_t st = (cudaStream_t)stream;
+    // bfloat16 weights with rows of whole 16-byte pieces (and x rows of whole float4s): the tensor-core form
+    if (w_dtype == EMBER_BF16 && K % 8 == 0 && ld_x % 4 == 0 && x_head % 4 == 0 && x_col % 4 == 0 && head_gemm_on_tensor_cores()) {
+        dim3 tgrid((T + HT_BM - 1) / HT_BM, (N + HT_BN - 1) / HT_BN, H);
+        if (out_dtype == EMBER_BF16) launch_kernel(head_gemm_tc_kernel<__nv_bfloat16>, tgrid, 128, 0, st, p);
+        else launch_kernel(head_gemm_tc_kernel<float>, tgrid, 128, 0, st, p);
+        return check_launch("head_gemm_tc");
+    }
+    dim3 grid((T + HG_BM - 1) / HG_BM, (N + HG_BN - 1) / HG_BN, H);
     if (w_dtype == EMBER_F32 && out_dtype == EMBER_F32) launch_kernel(head_gemm_kernel<float, float>, grid, 256, 0, st, p);
     else if (w_dtype == EMBER_BF16 && out_dtype == EMBER_BF16) launch_kernel(head_gemm_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, st, p);
     else if (w_dtype == EMBER_BF16 && out_dtype == EMBER_F32) launch_kernel(head_gemm_kernel<__nv_bfloat16, float>, grid, 256, 0, st, p);
