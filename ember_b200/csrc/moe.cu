@@ -12,7 +12,8 @@
 // Both products come in two forms: tiles of 32 slots x 64 outputs through shared memory (any sizes, any step), and,
 // for steps of few tokens, a streaming form in which a block keeps its (at most 16) rows in shared memory and every
 // warp streams whole weight rows past them in 16-byte pieces, so an expert's weights are read once at the rate of
-// the memory and only the rows that exist are multiplied.
+// the memory and only the rows that exist are multiplied (fp32 multiply-adds; for bfloat16 with K a multiple of 64 the
+// same on mma.sync, weights through per-warp cp.async stages).
 //
 // Nothing is read back by the host: the products' grids are sized for the most row tiles the step can have and blocks
 // beyond the tile list leave at once, so a decode step can be captured into a CUDA graph.  Every output row is a sum
@@ -335,6 +336,109 @@ __global__ void __launch_bounds__(MS_WARPS * 32) moe_stream_kernel(MoeGemmArgs p
     else moe_stream_rows<T, TO, GATED, 16>(p, xs, w, row0, rows, pair0);
 }
 
+// ------------------------------------------------------------- the streaming form on the tensor cores (bfloat16)
+// The same tiles of at most 16 slots.  A warp owns 16 weight rows and streams them 64 elements at a time through a
+// two-stage buffer of its own (cp.async, 128 contiguous bytes a row); the tile's rows of x wait in shared memory, 512
+// elements of K at a time.  mma.sync m16n8k16 with the weights as the row operand: D[weight row, slot], fp32 sums.  The
+// kernel does almost no arithmetic; what counts is that every warp always has a piece of its weight rows in flight.
+constexpr int MT_WARPS = 4, MT_KS = 64, MT_KC = 512, MT_WLD = MT_KS + 8, MT_XLD = MT_KC + 8;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(MT_WARPS * 32) moe_stream_tc_kernel(MoeGemmArgs p) {
+    __shared__ __align__(16) __nv_bfloat16 xs[MS_ROWS * MT_XLD];                    // the tile's rows, one chunk of K
+    __shared__ __align__(16) __nv_bfloat16 ws[MT_WARPS * 2 * 16 * MT_WLD];          // per warp: two stages of 16 x 64
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)blockIdx.x >= *p.n_tiles) return;
+    const int e = p.tile_expert[blockIdx.x], row0 = p.tile_row0[blockIdx.x];
+    const int rows = min(MS_ROWS, p.offsets[e + 1] - row0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int n0 = (blockIdx.y * MT_WARPS + warp) * 16;                              // the warp's first weight row
+    const __nv_bfloat16* w = (const __nv_bfloat16*)p.w + (size_t)e * p.w_expert;
+    const __nv_bfloat16* x = (const __nv_bfloat16*)p.x;
+    __nv_bfloat16* wb = ws + warp * 2 * 16 * MT_WLD;
+    const int steps = p.K / MT_KS;
+    auto issue = [&](int s) {
+        __nv_bfloat16* dst = wb + (s & 1) * 16 * MT_WLD;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int piece = lane + 32 * i, r = piece >> 3, c = (piece & 7) * 8;
+            __nv_bfloat16* d = dst + r * MT_WLD + c;
+            if (n0 + r < p.N) {
+                const uint32_t sa = (uint32_t)__cvta_generic_to_shared(d);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(w + (size_t)(n0 + r) * p.K + (size_t)s * MT_KS + c) : "memory");
+            } else {
+                *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float acc[2][4] = {};
+    issue(0);
+    for (int s = 0; s < steps; s++) {
+        if (s % (MT_KC / MT_KS) == 0) {
+            __syncthreads();                                    // the chunk before is consumed
+            const int k0 = s * MT_KS, kn = min(MT_KC, p.K - k0) / 8;
+            for (int idx = threadIdx.x; idx < MS_ROWS * kn; idx += blockDim.x) {
+                const int r = idx / kn, c = idx - r * kn;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (r < rows) {
+                    const int src = p.top > 0 ? p.pair_of_slot[row0 + r] / p.top : row0 + r;
+                    v = reinterpret_cast<const uint4*>(x + (size_t)src * p.ld_x + k0)[c];
+                }
+                *reinterpret_cast<uint4*>(xs + r * MT_XLD + c * 8) = v;
+            }
+            __syncthreads();
+        }
+        if (s + 1 < steps) {
+            issue(s + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncwarp();
+        const __nv_bfloat16* wa = wb + (s & 1) * 16 * MT_WLD + (lane & 15) * MT_WLD + (lane >> 4) * 8;
+        const __nv_bfloat16* xb = xs + ((lane >> 4) * 8 + (lane & 7)) * MT_XLD + (s % (MT_KC / MT_KS)) * MT_KS + ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int kk = 0; kk < MT_KS; kk += 16) {
+            uint32_t af[4], bf[4];
+            ldsm_x4(af, wa + kk);
+            ldsm_x4(bf, xb + kk);
+            mma_16816(acc[0], af, bf[0], bf[1]);                // slots 0..7
+            mma_16816(acc[1], af, bf[2], bf[3]);                // slots 8..15
+        }
+        __syncwarp();
+    }
+    // acc[j][0..1]: weight row g, slots 8 j + 2 t, + 1;  acc[j][2..3]: weight row g + 8
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+#pragma unroll
+        for (int half = 0; half < 2; half++)
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const float v = acc[j][2 * half + c];
+                const int n = n0 + g + 8 * half, slot = 8 * j + 2 * t + c;
+                if (GATED) {
+                    const float up = __shfl_xor_sync(0xffffffffu, v, 4);     // the odd row beside this even one
+                    if ((g & 1) == 0 && n < p.N && slot < rows) {
+                        const float gt = fminf(v, p.limit), u = fminf(fmaxf(up, -p.limit), p.limit);
+                        ((TO*)p.out)[(size_t)(row0 + slot) * p.ld_o + (n >> 1)] = from_float<TO>(gt / (1.0f + expf(-p.alpha * gt)) * (u + 1.0f));
+                    }
+                } else if (n < p.N && slot < rows) {
+                    ((TO*)p.out)[(size_t)(row0 + slot) * p.ld_o + n] = from_float<TO>(v);
+                }
+            }
+}
+
 // xs[slot] = x[token of the slot's pair]: the rows of each expert side by side, for products that want plain matrices.
 __global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ pair_of_slot, int top, uint4* __restrict__ xs,
                                   int row16) {
@@ -446,9 +550,18 @@ EMBER_API int ember_moe_stream(const void* x, int x_dtype, int ld_x, const void*
     const size_t smem = (size_t)MS_ROWS * K * elem;
     if (smem > 200 * 1024) return fail("moe_stream: %d rows of %d do not fit in shared memory", MS_ROWS, K);
     MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha};
-    dim3 grid(max_tiles, ((N + 1) / 2 + MS_PAIRS - 1) / MS_PAIRS);
     cudaStream_t st = (cudaStream_t)stream;
     const int key = x_dtype * 100 + w_dtype * 10 + out_dtype;       // F32 = 0, BF16 = 1
+    static int tc_on = -1;
+    if (tc_on < 0) { const char* ev = getenv("EMBER_MOE_STREAM_TC"); tc_on = (ev && ev[0] == '0') ? 0 : 1; }
+    if (tc_on && x_dtype == EMBER_BF16 && w_dtype == EMBER_BF16 && K % MT_KS == 0) {     // the tensor-core form
+        dim3 tgrid(max_tiles, (N + MT_WARPS * 16 - 1) / (MT_WARPS * 16));
+        if (gated && out_dtype == EMBER_BF16) launch_kernel(moe_stream_tc_kernel<__nv_bfloat16, true>, tgrid, MT_WARPS * 32, 0, st, p);
+        else if (!gated && out_dtype == EMBER_F32) launch_kernel(moe_stream_tc_kernel<float, false>, tgrid, MT_WARPS * 32, 0, st, p);
+        else return fail("moe_stream: unsupported dtypes %d", key);
+        return check_launch("moe_stream_tc");
+    }
+    dim3 grid(max_tiles, ((N + 1) / 2 + MS_PAIRS - 1) / MS_PAIRS);
     auto run = [&](auto kernel) -> int {
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
