@@ -1,6 +1,6 @@
 // Recurrent mixers over a ragged batch: a short causal convolution whose last inputs are carried per request, and
-// three matrix-state recurrences (delta rule with a decay per key channel, matrix memory with exponential gating,
-// selective state space with a scalar decay per head).  Everything that enters a recurrence is fp32: decays and
+// four matrix-state recurrences (delta rule with a decay per key channel, matrix memory with exponential gating,
+// selective state space with a scalar decay per head, gated linear attention with a decay per key channel).  Everything that enters a recurrence is fp32: decays and
 // their logarithms, softplus and exponentials, gates, unit norms, the state itself.
 //
 // A step's tokens are S runs (query_start [S + 1]); run s belongs to state slot slots[s].  A recurrence kernel runs
